@@ -189,6 +189,8 @@ void register_builtin_architectures() {
   register_sinezen_architecture();
   extern void register_sesuzen_architecture();     // config/sesuzen.cc
   register_sesuzen_architecture();
+  extern void register_sobezen_architecture();     // config/sobezen.cc
+  register_sobezen_architecture();
 }
 
 }  // namespace llm

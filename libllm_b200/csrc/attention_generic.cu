@@ -1,5 +1,5 @@
-// Causal grouped-query attention over the paged cache, any head size up to 256 (values may
-// have another width than keys), any number of heads and groups; optional sliding window,
+// Causal grouped-query attention over the paged cache, any head size up to 1,024 (values may
+// have another width than keys, or be the first channels of the key rows themselves: v_ld), any number of heads and groups; optional sliding window,
 // optional block mask (a query sees only keys of its own block of `block` positions, blocks
 // counted from position 0), optionally the first `sink` positions of the sequence kept visible
 // beyond the window (at their true positions), optional gate per (token, head) on the result (multiplied by
@@ -23,7 +23,7 @@
 LLM_DEFINE_LAST_ERROR(llm_attention_generic_last_error)
 
 constexpr int WARPS = 4;
-constexpr int MAX_D = 256;
+constexpr int MAX_D_SMALL = 256, MAX_D_LARGE = 1024;
 
 __device__ __forceinline__ float dot_row(const float *q, const float *k, int d, bool vec) {
   float acc = 0.f;
@@ -59,7 +59,7 @@ __device__ __forceinline__ float dot_row(const float *q, const __nv_bfloat16 *k,
   return acc;
 }
 
-template <typename T>
+template <typename T, int MAX_D>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_generic_kernel(const T *__restrict__ q, long long q_stride, T *__restrict__ out,
                          long long out_stride, const T *__restrict__ kcache,
@@ -67,7 +67,7 @@ attention_generic_kernel(const T *__restrict__ q, long long q_stride, T *__restr
                          const int *__restrict__ tok_pos, const int *__restrict__ page_table,
                          int pt_stride, int n_tokens, int n_heads, int n_kv, int d, int dv, int page_size,
                          int window, int block, int sink, float scale, const float *__restrict__ gate,
-                         long long gate_stride, int vec) {
+                         long long gate_stride, int vec, int v_ld) {
   __shared__ __align__(16) float q_s[WARPS][MAX_D];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long w = (long long)blockIdx.x * WARPS + warp;
@@ -111,7 +111,7 @@ attention_generic_kernel(const T *__restrict__ q, long long q_stride, T *__restr
         const float pv = __shfl_sync(0xffffffffu, pj, jj);
         const int key = kb + jj;
         const int page = pt[key / page_size];
-        const T *vrow = vcache + (((size_t)page * n_kv + kvh) * page_size + (key % page_size)) * dv;
+        const T *vrow = vcache + (((size_t)page * n_kv + kvh) * page_size + (key % page_size)) * v_ld;
 #pragma unroll
         for (int i = 0; i < MAX_D / 32; ++i) {
           const int c = lane + 32 * i;
@@ -131,15 +131,19 @@ attention_generic_kernel(const T *__restrict__ q, long long q_stride, T *__restr
   }
 }
 
-LLM_EXPORT int llm_attention_generic(int dtype, const void *q, long long q_stride, void *out,
-                                     long long out_stride, const void *kcache, const void *vcache,
-                                     const int *tok_seq, const int *tok_pos, const int *page_table,
-                                     int pt_stride, int n_tokens, int n_heads, int n_kv, int d, int dv,
-                                     int page_size, int window, int block, int sink, float scale, const float *gate,
-                                     long long gate_stride, cudaStream_t stream) {
+// v_ld: channels between two value rows of the value storage (dv for a storage of its own; the key rows' width
+// when the values are the first dv channels of the keys and vcache is kcache).
+LLM_EXPORT int llm_attention_generic_ld(int dtype, const void *q, long long q_stride, void *out,
+                                        long long out_stride, const void *kcache, const void *vcache,
+                                        const int *tok_seq, const int *tok_pos, const int *page_table,
+                                        int pt_stride, int n_tokens, int n_heads, int n_kv, int d, int dv, int v_ld,
+                                        int page_size, int window, int block, int sink, float scale, const float *gate,
+                                        long long gate_stride, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0, "attention: bad head counts %d/%d", n_heads, n_kv);
-  LLM_REQUIRE(d > 0 && d <= MAX_D && dv > 0 && dv <= MAX_D, "attention: head sizes %d / %d are not supported (up to %d)", d, dv, MAX_D);
+  LLM_REQUIRE(d > 0 && d <= MAX_D_LARGE && dv > 0 && dv <= MAX_D_LARGE, "attention: head sizes %d / %d are not supported (up to %d)", d, dv,
+              MAX_D_LARGE);
+  LLM_REQUIRE(v_ld >= dv, "attention: value rows of %d channels in a storage of %d a row", dv, v_ld);
   LLM_REQUIRE(window >= 0 && block >= 0 && sink >= 0, "attention: bad window, block or number of kept first positions");
   LLM_REQUIRE(sink == 0 || block == 0, "attention: kept first positions go with a window, not with a block mask");
   // 16-byte loads of key rows where rows start on such a boundary
@@ -147,19 +151,27 @@ LLM_EXPORT int llm_attention_generic(int dtype, const void *q, long long q_strid
   const long long warps = (long long)n_tokens * n_heads;
   const long long blocks = (warps + WARPS - 1) / WARPS;
   LLM_REQUIRE(blocks < 2147483647LL, "attention: too many tokens for one launch");
-  if (dtype == LLM_F32) {
-    attention_generic_kernel<float><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
-        (const float *)q, q_stride, (float *)out, out_stride, (const float *)kcache, (const float *)vcache,
-        tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, n_kv, d, dv, page_size, window, block, sink, scale,
-        gate, gate_stride, vec);
-  } else if (dtype == LLM_BF16) {
-    attention_generic_kernel<__nv_bfloat16><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
-        (const __nv_bfloat16 *)q, q_stride, (__nv_bfloat16 *)out, out_stride, (const __nv_bfloat16 *)kcache,
-        (const __nv_bfloat16 *)vcache, tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, n_kv, d, dv,
-        page_size, window, block, sink, scale, gate, gate_stride, vec);
-  } else {
-    LLM_FAIL("attention: unknown dtype %d", dtype);
-  }
+  const bool small = d <= MAX_D_SMALL && dv <= MAX_D_SMALL;
+#define GENERIC_GO(T, MAXD)                                                                                              \
+  attention_generic_kernel<T, MAXD><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(                                          \
+      (const T *)q, q_stride, (T *)out, out_stride, (const T *)kcache, (const T *)vcache, tok_seq, tok_pos, page_table, pt_stride, \
+      n_tokens, n_heads, n_kv, d, dv, page_size, window, block, sink, scale, gate, gate_stride, vec, v_ld)
+  if (dtype == LLM_F32 && small) GENERIC_GO(float, MAX_D_SMALL);
+  else if (dtype == LLM_F32) GENERIC_GO(float, MAX_D_LARGE);
+  else if (dtype == LLM_BF16 && small) GENERIC_GO(__nv_bfloat16, MAX_D_SMALL);
+  else if (dtype == LLM_BF16) GENERIC_GO(__nv_bfloat16, MAX_D_LARGE);
+  else LLM_FAIL("attention: unknown dtype %d", dtype);
+#undef GENERIC_GO
   LLM_CHECK_LAUNCH("attention_generic");
   return LLM_OK;
+}
+
+LLM_EXPORT int llm_attention_generic(int dtype, const void *q, long long q_stride, void *out,
+                                     long long out_stride, const void *kcache, const void *vcache,
+                                     const int *tok_seq, const int *tok_pos, const int *page_table,
+                                     int pt_stride, int n_tokens, int n_heads, int n_kv, int d, int dv,
+                                     int page_size, int window, int block, int sink, float scale, const float *gate,
+                                     long long gate_stride, cudaStream_t stream) {
+  return llm_attention_generic_ld(dtype, q, q_stride, out, out_stride, kcache, vcache, tok_seq, tok_pos, page_table, pt_stride,
+                                  n_tokens, n_heads, n_kv, d, dv, dv, page_size, window, block, sink, scale, gate, gate_stride, stream);
 }

@@ -50,6 +50,7 @@ FAMILIES: Dict[str, dict] = {
     "rope": dict(sources=["rope.cu"], headers=["common.cuh"]),
     "recurrent": dict(sources=["recurrent.cu"], headers=["common.cuh"]),
     "attention_generic": dict(sources=["attention_generic.cu"], headers=["common.cuh"]),
+    "latent": dict(sources=["latent.cu"], headers=["common.cuh"]),
     "sampling": dict(sources=["sampling.cu"], headers=["common.cuh"]),
     "moe": dict(sources=["moe.cu"], headers=["common.cuh", "mma_tiles.cuh"]),
     "moe_tc": dict(sources=["moe_tc.cu"], headers=["common.cuh", "tc_common.cuh"]),

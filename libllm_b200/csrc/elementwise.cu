@@ -121,13 +121,16 @@ LLM_EXPORT int llm_gather_words(const int *src1, int n1, const int *src2, int n2
 // ---------------------------------------------------------------- add + rmsnorm
 // For each output row i (source row r = rows ? rows[i] : i):
 //   v = resid[r] + sum_p delta[p][r]      (32-bit; parts added in index order)
+//       with col_scale / col_bias (vectors over the columns, either may be null):
+//       v = resid[r] + (sum_p delta[p][r] + col_bias) * col_scale
 //   if (!rows) resid[r] = v               (the residual stream moves on)
 //   out[i] = v * w * rsqrt(mean(v^2) + eps)   (skipped when out is null)
 template <typename TD, typename TO, int THREADS>
 __global__ void add_rmsnorm_kernel(float *__restrict__ resid, const TD *__restrict__ delta,
                                    int n_parts, size_t part_stride, const float *__restrict__ weight,
                                    float eps, TO *__restrict__ out, const int *__restrict__ rows,
-                                   int hidden) {
+                                   int hidden, const float *__restrict__ col_scale,
+                                   const float *__restrict__ col_bias) {
   extern __shared__ float row_buf[];   // hidden floats
   __shared__ float scratch[THREADS / 32 + 1];
   grid_dependents_launch();
@@ -138,7 +141,15 @@ __global__ void add_rmsnorm_kernel(float *__restrict__ resid, const TD *__restri
   float ss = 0.f;
   for (int c = threadIdx.x; c < hidden; c += THREADS) {
     float v = x[c];
-    for (int p = 0; p < n_parts; ++p) v += to_float(delta[p * part_stride + (size_t)r * hidden + c]);
+    if (col_scale || col_bias) {
+      float d = 0.f;
+      for (int p = 0; p < n_parts; ++p) d += to_float(delta[p * part_stride + (size_t)r * hidden + c]);
+      if (col_bias) d += col_bias[c];
+      if (col_scale) d *= col_scale[c];
+      if (n_parts > 0) v += d;
+    } else {
+      for (int p = 0; p < n_parts; ++p) v += to_float(delta[p * part_stride + (size_t)r * hidden + c]);
+    }
     row_buf[c] = v;
     if (!rows && n_parts > 0) x[c] = v;
     ss += v * v;
@@ -160,17 +171,27 @@ template <typename TD, typename TO, int THREADS, int VPT, int MAXP>
 __global__ void __launch_bounds__(THREADS)
 add_rmsnorm_vec_kernel(float *__restrict__ resid, const TD *__restrict__ delta, int n_parts,
                        size_t part_stride, const float *__restrict__ weight, float eps,
-                       TO *__restrict__ out, const int *__restrict__ rows, int hidden) {
+                       TO *__restrict__ out, const int *__restrict__ rows, int hidden,
+                       const float *__restrict__ col_scale, const float *__restrict__ col_bias) {
   __shared__ float scratch[THREADS / 32 + 1];
   grid_dependents_launch();
   const int i = blockIdx.x;
   const int n4 = hidden / 4;
-  float4 v[VPT], w[VPT], d[VPT][MAXP];
+  const bool scaled = col_scale || col_bias;
+  float4 v[VPT], w[VPT], d[VPT][MAXP], cs[VPT], cb[VPT];
   if (out) {                             // the norm's weight does not depend on the kernel before
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
       const int c4 = threadIdx.x + j * THREADS;
       if (c4 < n4) w[j] = ld4(weight + 4 * c4);
+    }
+  }
+  if (scaled) {                          // weights too
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int c4 = threadIdx.x + j * THREADS;
+      cs[j] = (col_scale && c4 < n4) ? ld4(col_scale + 4 * c4) : make_float4(1.f, 1.f, 1.f, 1.f);
+      cb[j] = (col_bias && c4 < n4) ? ld4(col_bias + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }
   grid_dependency_wait();
@@ -191,14 +212,30 @@ add_rmsnorm_vec_kernel(float *__restrict__ resid, const TD *__restrict__ delta, 
   for (int j = 0; j < VPT; ++j) {
     const int c4 = threadIdx.x + j * THREADS;
     if (c4 < n4) {
+      if (scaled && n_parts > 0) {         // the parts' sum first, then bias and scale, then the stream
+        float4 t = d[j][0];
 #pragma unroll
-      for (int p = 0; p < MAXP; ++p)
-        if (p < n_parts) {
-          v[j].x += d[j][p].x;
-          v[j].y += d[j][p].y;
-          v[j].z += d[j][p].z;
-          v[j].w += d[j][p].w;
-        }
+        for (int p = 1; p < MAXP; ++p)
+          if (p < n_parts) {
+            t.x += d[j][p].x;
+            t.y += d[j][p].y;
+            t.z += d[j][p].z;
+            t.w += d[j][p].w;
+          }
+        v[j].x += (t.x + cb[j].x) * cs[j].x;
+        v[j].y += (t.y + cb[j].y) * cs[j].y;
+        v[j].z += (t.z + cb[j].z) * cs[j].z;
+        v[j].w += (t.w + cb[j].w) * cs[j].w;
+      } else {
+#pragma unroll
+        for (int p = 0; p < MAXP; ++p)
+          if (p < n_parts) {
+            v[j].x += d[j][p].x;
+            v[j].y += d[j][p].y;
+            v[j].z += d[j][p].z;
+            v[j].w += d[j][p].w;
+          }
+      }
       if (!rows && n_parts > 0) st4(x + 4 * c4, v[j]);
       ss += v[j].x * v[j].x;
       ss += v[j].y * v[j].y;
@@ -222,11 +259,13 @@ add_rmsnorm_vec_kernel(float *__restrict__ resid, const TD *__restrict__ delta, 
 template <typename TD, typename TO>
 static int launch_add_rmsnorm(float *resid, const void *delta, int n_parts, size_t part_stride,
                               const float *weight, float eps, void *out, const int *rows, int n_rows,
-                              int hidden, cudaStream_t stream) {
+                              int hidden, cudaStream_t stream, const float *col_scale = nullptr,
+                              const float *col_bias = nullptr) {
   constexpr int THREADS = 256;
   constexpr int VPT = 4;
   const bool aligned = hidden % 4 == 0 && (uintptr_t)resid % 16 == 0 && (uintptr_t)delta % 16 == 0 &&
-                       (uintptr_t)weight % 16 == 0 && (uintptr_t)out % 16 == 0 && part_stride % 4 == 0;
+                       (uintptr_t)weight % 16 == 0 && (uintptr_t)out % 16 == 0 && part_stride % 4 == 0 &&
+                       (uintptr_t)col_scale % 16 == 0 && (uintptr_t)col_bias % 16 == 0;
   if (aligned && hidden <= 4 * VPT * THREADS && n_parts <= 16) {
     // one instantiation per bound on the parts: registers for eight parts cost a prompt step
     // (one part, thousands of rows) a third of its speed
@@ -234,7 +273,8 @@ static int launch_add_rmsnorm(float *resid, const void *delta, int n_parts, size
     // loads of a row are in flight from more warps at once.
 #define ADDNORM_GO2(T_, V_, MAXP)                                                                        \
   llm_launch(add_rmsnorm_vec_kernel<TD, TO, T_, V_, MAXP>, n_rows, T_, 0, stream, resid,                 \
-             (const TD *)delta, n_parts, part_stride, weight, eps, (TO *)out, rows, hidden)
+             (const TD *)delta, n_parts, part_stride, weight, eps, (TO *)out, rows, hidden, col_scale,   \
+             col_bias)
 #define ADDNORM_GO(MAXP)                                                                                 \
   do {                                                                                                   \
     if (hidden <= 2048) ADDNORM_GO2(512, 1, MAXP);                                                       \
@@ -257,33 +297,42 @@ static int launch_add_rmsnorm(float *resid, const void *delta, int n_parts, size
     LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "add_rmsnorm attribute");
   }
   llm_launch(kern, n_rows, THREADS, smem, stream, resid, (const TD *)delta, n_parts, part_stride, weight, eps,
-             (TO *)out, rows, hidden);
+             (TO *)out, rows, hidden, col_scale, col_bias);
   LLM_CHECK_LAUNCH("add_rmsnorm");
   return LLM_OK;
 }
 
+// With a scale and a bias over the columns (either may be null) on what is added.
 // delta_dtype: type of delta; out_dtype: type of out.  delta may be null (n_parts 0),
 // out may be null (add only), rows may be null (all rows, residual written back).
-LLM_EXPORT int llm_add_rmsnorm(float *resid, const void *delta, int delta_dtype, int n_parts,
+LLM_EXPORT int llm_add_rmsnorm_scaled(float *resid, const void *delta, int delta_dtype, int n_parts,
                                long long part_stride, const float *weight, float eps, void *out,
                                int out_dtype, const int *rows, int n_rows, int hidden,
-                               cudaStream_t stream) {
+                               const float *col_scale, const float *col_bias, cudaStream_t stream) {
   if (n_rows == 0) return LLM_OK;
   LLM_REQUIRE(n_rows > 0 && hidden > 0 && n_parts >= 0, "add_rmsnorm: bad sizes");
   LLM_REQUIRE(out == nullptr || weight != nullptr, "add_rmsnorm: a norm needs its weight");
   if (!delta) n_parts = 0;
   if (delta_dtype == LLM_F32 && out_dtype == LLM_F32)
-    return launch_add_rmsnorm<float, float>(resid, delta, n_parts, part_stride, weight, eps, out, rows, n_rows, hidden, stream);
+    return launch_add_rmsnorm<float, float>(resid, delta, n_parts, part_stride, weight, eps, out, rows, n_rows, hidden, stream, col_scale, col_bias);
   if (delta_dtype == LLM_F32 && out_dtype == LLM_BF16)
-    return launch_add_rmsnorm<float, __nv_bfloat16>(resid, delta, n_parts, part_stride, weight, eps, out, rows, n_rows, hidden, stream);
+    return launch_add_rmsnorm<float, __nv_bfloat16>(resid, delta, n_parts, part_stride, weight, eps, out, rows, n_rows, hidden, stream, col_scale, col_bias);
   if (delta_dtype == LLM_BF16 && out_dtype == LLM_BF16)
-    return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, n_parts, part_stride, weight, eps, out, rows, n_rows, hidden, stream);
+    return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, n_parts, part_stride, weight, eps, out, rows, n_rows, hidden, stream, col_scale, col_bias);
   if (delta_dtype == LLM_BF16 && out_dtype == LLM_F32)
-    return launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, n_parts, part_stride, weight, eps, out, rows, n_rows, hidden, stream);
+    return launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, n_parts, part_stride, weight, eps, out, rows, n_rows, hidden, stream, col_scale, col_bias);
   LLM_FAIL("add_rmsnorm: unknown dtypes %d, %d", delta_dtype, out_dtype);
 }
 
 // ---------------------------------------------------------------- add + layer norm
+LLM_EXPORT int llm_add_rmsnorm(float *resid, const void *delta, int delta_dtype, int n_parts,
+                               long long part_stride, const float *weight, float eps, void *out,
+                               int out_dtype, const int *rows, int n_rows, int hidden,
+                               cudaStream_t stream) {
+  return llm_add_rmsnorm_scaled(resid, delta, delta_dtype, n_parts, part_stride, weight, eps, out, out_dtype, rows, n_rows,
+                                hidden, nullptr, nullptr, stream);
+}
+
 // As add_rmsnorm, with the norm  out = (v - mean) / sqrt(var + eps) * w + b,  var the mean of the
 // squared deviations (two passes over the row, which is kept in shared memory; sums in 32-bit in
 // the block's fixed order).
@@ -616,30 +665,45 @@ LLM_EXPORT int llm_add_layernorm_conv(float *resid, const void *delta, int delta
 // stream of the rows that anything still reads, when the others are done with.
 template <typename TD>
 __global__ void gather_rows_add_kernel(const float *__restrict__ resid, const TD *__restrict__ delta, int n_parts,
-                                       size_t part_stride, const int *__restrict__ rows, float *__restrict__ out, int hidden) {
+                                       size_t part_stride, const int *__restrict__ rows, float *__restrict__ out, int hidden,
+                                       const float *__restrict__ col_scale, const float *__restrict__ col_bias) {
   grid_dependents_launch();
   grid_dependency_wait();
   const int i = blockIdx.x;
   const size_t r = (size_t)rows[i];
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float v = resid[r * hidden + c];
-    for (int p = 0; p < n_parts; ++p) v += to_float(delta[p * part_stride + r * hidden + c]);
+    if (col_scale || col_bias) {
+      float d = 0.f;
+      for (int p = 0; p < n_parts; ++p) d += to_float(delta[p * part_stride + r * hidden + c]);
+      if (col_bias) d += col_bias[c];
+      if (col_scale) d *= col_scale[c];
+      if (n_parts > 0) v += d;
+    } else {
+      for (int p = 0; p < n_parts; ++p) v += to_float(delta[p * part_stride + r * hidden + c]);
+    }
     out[(size_t)i * hidden + c] = v;
   }
 }
 
-LLM_EXPORT int llm_gather_rows_add(const float *resid, const void *delta, int delta_dtype, int n_parts, long long part_stride,
-                                   const int *rows, int n_rows, float *out, int hidden, cudaStream_t stream) {
+LLM_EXPORT int llm_gather_rows_add_scaled(const float *resid, const void *delta, int delta_dtype, int n_parts, long long part_stride,
+                                          const int *rows, int n_rows, float *out, int hidden, const float *col_scale,
+                                          const float *col_bias, cudaStream_t stream) {
   if (n_rows == 0) return LLM_OK;
   LLM_REQUIRE(n_rows > 0 && hidden > 0 && n_parts >= 0 && rows != nullptr && out != nullptr, "gather_rows_add: bad arguments");
   if (!delta) n_parts = 0;
   if (delta_dtype == LLM_BF16 && n_parts > 0)
     LLM_CHECK_CUDA(llm_launch(gather_rows_add_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, resid, (const __nv_bfloat16 *)delta,
-                              n_parts, (size_t)part_stride, rows, out, hidden), "gather_rows_add launch");
+                              n_parts, (size_t)part_stride, rows, out, hidden, col_scale, col_bias), "gather_rows_add launch");
   else
     LLM_CHECK_CUDA(llm_launch(gather_rows_add_kernel<float>, dim3(n_rows), dim3(256), 0, stream, resid, (const float *)delta, n_parts,
-                              (size_t)part_stride, rows, out, hidden), "gather_rows_add launch");
+                              (size_t)part_stride, rows, out, hidden, col_scale, col_bias), "gather_rows_add launch");
   return LLM_OK;
+}
+
+LLM_EXPORT int llm_gather_rows_add(const float *resid, const void *delta, int delta_dtype, int n_parts, long long part_stride,
+                                   const int *rows, int n_rows, float *out, int hidden, cudaStream_t stream) {
+  return llm_gather_rows_add_scaled(resid, delta, delta_dtype, n_parts, part_stride, rows, n_rows, out, hidden, nullptr, nullptr, stream);
 }
 
 // ---------------------------------------------------------------- swiglu
@@ -697,6 +761,81 @@ LLM_EXPORT int llm_swiglu(int in_dtype, int dtype, const void *gu, void *out, in
   else LLM_FAIL("swiglu: unsupported dtypes in %d out %d", in_dtype, dtype);
 #undef SWIGLU_GO
   LLM_CHECK_LAUNCH("swiglu");
+  return LLM_OK;
+}
+
+// ---------------------------------------------------------------- clamped gated unit
+// Rows [gate (inter) | up (inter)] of a stacked product (32-bit or bfloat16), biases of 2 * inter 32-bit
+// values (null: none) added here, in 32-bit, so that the product runs without them:
+//   g = min(gate + b_g, limit), u = clamp(up + b_u, -limit, limit), out = g * sigmoid(slope * g) * (u + up_shift).
+// limit <= 0: no bounds.
+__device__ __forceinline__ float clamped_glu_one(float g, float u, float limit, float slope, float up_shift) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+  }
+  return g / (1.f + expf(-slope * g)) * (u + up_shift);
+}
+
+template <typename TI, typename T>
+__global__ void clamped_glu_kernel(const TI *__restrict__ gu, long long ld, const float *__restrict__ bias, T *__restrict__ out,
+                                   int inter, size_t total, float limit, float slope, float up_shift) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter;
+    const int i = (int)(idx - t * inter);
+    const float g = to_float(gu[t * ld + i]) + (bias ? bias[i] : 0.f);
+    const float u = to_float(gu[t * ld + inter + i]) + (bias ? bias[inter + i] : 0.f);
+    out[idx] = from_float<T>(clamped_glu_one(g, u, limit, slope, up_shift));
+  }
+}
+
+// Four values per thread (widths that are a multiple of 4, 16-byte aligned rows).
+template <typename TI, typename T>
+__global__ void clamped_glu_vec_kernel(const TI *__restrict__ gu, long long ld, const float *__restrict__ bias, T *__restrict__ out,
+                                       int inter4, size_t total4, float limit, float slope, float up_shift) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter4;
+    const int i = (int)(idx - t * inter4) * 4;
+    const TI *row = gu + t * ld;
+    float4 g = ld4(row + i), u = ld4(row + 4 * (size_t)inter4 + i);
+    if (bias) {
+      const float4 bg = ld4(bias + i), bu = ld4(bias + 4 * (size_t)inter4 + i);
+      g = make_float4(g.x + bg.x, g.y + bg.y, g.z + bg.z, g.w + bg.w);
+      u = make_float4(u.x + bu.x, u.y + bu.y, u.z + bu.z, u.w + bu.w);
+    }
+    st4(out + idx * 4, make_float4(clamped_glu_one(g.x, u.x, limit, slope, up_shift), clamped_glu_one(g.y, u.y, limit, slope, up_shift),
+                                   clamped_glu_one(g.z, u.z, limit, slope, up_shift), clamped_glu_one(g.w, u.w, limit, slope, up_shift)));
+  }
+}
+
+LLM_EXPORT int llm_clamped_glu(int in_dtype, int dtype, const void *gu, long long ld, const float *bias, void *out, int n_tokens,
+                               int inter, float limit, float slope, float up_shift, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && inter > 0 && ld >= 2LL * inter, "clamped_glu: bad sizes");
+  const int threads = 256;
+  const bool vec = inter % 4 == 0 && ld % 8 == 0 && (uintptr_t)gu % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)bias % 16 == 0;
+  const size_t total = vec ? (size_t)n_tokens * (inter / 4) : (size_t)n_tokens * inter;
+  size_t blocks = (total + threads - 1) / threads;
+  if (blocks > (size_t)sm_count() * 32) blocks = (size_t)sm_count() * 32;
+#define CGLU_GO(TI, T)                                                                                                   \
+  do {                                                                                                                   \
+    if (vec)                                                                                                             \
+      llm_launch(clamped_glu_vec_kernel<TI, T>, (unsigned)blocks, threads, 0, stream, (const TI *)gu, ld, bias, (T *)out, inter / 4, \
+                 total, limit, slope, up_shift);                                                                         \
+    else                                                                                                                 \
+      llm_launch(clamped_glu_kernel<TI, T>, (unsigned)blocks, threads, 0, stream, (const TI *)gu, ld, bias, (T *)out, inter, total, \
+                 limit, slope, up_shift);                                                                                \
+  } while (0)
+  if (in_dtype == LLM_F32 && dtype == LLM_F32) CGLU_GO(float, float);
+  else if (in_dtype == LLM_F32 && dtype == LLM_BF16) CGLU_GO(float, __nv_bfloat16);
+  else if (in_dtype == LLM_BF16 && dtype == LLM_BF16) CGLU_GO(__nv_bfloat16, __nv_bfloat16);
+  else LLM_FAIL("clamped_glu: unsupported dtypes in %d out %d", in_dtype, dtype);
+#undef CGLU_GO
+  LLM_CHECK_LAUNCH("clamped_glu");
   return LLM_OK;
 }
 

@@ -143,9 +143,12 @@ LLM_KERNEL("elementwise", llm_add_layernorm, float *, const void *, int, int, lo
            int, const int *, int, int, cudaStream_t)
 LLM_KERNEL("elementwise", llm_copy_words, const int *, int *, int, cudaStream_t)
 LLM_KERNEL("elementwise", llm_gather_words, const int *, int, const int *, int, int *, cudaStream_t)
-LLM_KERNEL("elementwise", llm_add_rmsnorm, float *, const void *, int, int, long long, const float *, float, void *, int,
-           const int *, int, int, cudaStream_t)
-LLM_KERNEL("elementwise", llm_gather_rows_add, const float *, const void *, int, int, long long, const int *, int, float *, int, cudaStream_t)
+LLM_KERNEL("elementwise", llm_add_rmsnorm_scaled, float *, const void *, int, int, long long, const float *, float, void *, int,
+           const int *, int, int, const float *, const float *, cudaStream_t)
+LLM_KERNEL("elementwise", llm_gather_rows_add_scaled, const float *, const void *, int, int, long long, const int *, int, float *, int,
+           const float *, const float *, cudaStream_t)
+LLM_KERNEL("elementwise", llm_clamped_glu, int, int, const void *, long long, const float *, void *, int, int, float, float, float,
+           cudaStream_t)
 LLM_KERNEL("elementwise", llm_swiglu, int, int, const void *, void *, int, int, cudaStream_t)
 LLM_KERNEL("elementwise", llm_scale_rows, float *, long long, float, cudaStream_t)
 LLM_KERNEL("elementwise", llm_logit_transform, float *, long long, float, float, cudaStream_t)
@@ -158,6 +161,8 @@ void embedding(DType dt, const void *table, const int *tokens, const int *fed_to
 }
 void add_layernorm(float *resid, const Act *delta, const float *weight, const float *bias, float eps, void *out, DType out_dtype,
                    const int *rows, int n_rows, int hidden, cudaStream_t s) {
+  if (delta && (delta->col_scale || delta->col_bias))
+    LLM_THROW(Unsupported, "add_layernorm: a pending addition with a scale or a bias over its columns is taken by the RMS norm's pass only");
   const bool has = delta && delta->data;
   LLM_CALL("elementwise", llm_add_layernorm, resid, has ? delta->data : nullptr, has ? code(delta->dtype) : 0,
            has ? delta->parts : 0, has ? (long long)delta->part_stride : 0, weight, bias, eps, out, code(out_dtype), rows, n_rows,
@@ -170,14 +175,16 @@ void gather_words(const int *src1, int n1, const int *src2, int n2, int *dst, cu
 void add_rmsnorm(float *resid, const Act *delta, const float *weight, float eps, void *out, DType out_dtype, const int *rows,
                  int n_rows, int hidden, cudaStream_t s) {
   const bool has = delta && delta->data;
-  LLM_CALL("elementwise", llm_add_rmsnorm, resid, has ? delta->data : nullptr, has ? code(delta->dtype) : 0,
+  LLM_CALL("elementwise", llm_add_rmsnorm_scaled, resid, has ? delta->data : nullptr, has ? code(delta->dtype) : 0,
            has ? delta->parts : 0, has ? (long long)delta->part_stride : 0, weight, eps, out, code(out_dtype), rows, n_rows,
-           hidden, s);
+           hidden, has ? delta->col_scale : nullptr, has ? delta->col_bias : nullptr, s);
 }
 LLM_KERNEL("elementwise", llm_add_layernorm_conv, float *, const void *, int, int, long long, const float *, const float *, float, void *,
            int, int, int, const float *, void *, const int *, int, cudaStream_t)
 void add_layernorm_conv(float *resid, const Act *delta, const float *weight, const float *bias, float eps, void *out, DType out_dtype,
                         int n_rows, int hidden, const float *conv_w, void *state, const int *seq_slot, int taps, cudaStream_t s) {
+  if (delta && (delta->col_scale || delta->col_bias))
+    LLM_THROW(Unsupported, "add_layernorm_conv: a pending addition with a scale or a bias over its columns is taken by the RMS norm's pass only");
   const bool has = delta && delta->data;
   LLM_CALL("elementwise", llm_add_layernorm_conv, resid, has ? delta->data : nullptr, has ? code(delta->dtype) : 0,
            has ? delta->parts : 0, has ? (long long)delta->part_stride : 0, weight, bias, eps, out, code(out_dtype), n_rows, hidden,
@@ -185,12 +192,19 @@ void add_layernorm_conv(float *resid, const Act *delta, const float *weight, con
 }
 void gather_rows_add(const float *resid, const Act *delta, const int *rows, int n_rows, float *out, int hidden, cudaStream_t s) {
   const bool has = delta && delta->data;
-  LLM_CALL("elementwise", llm_gather_rows_add, resid, has ? delta->data : nullptr, has ? code(delta->dtype) : 0, has ? delta->parts : 0,
-           has ? (long long)delta->part_stride : 0, rows, n_rows, out, hidden, s);
+  LLM_CALL("elementwise", llm_gather_rows_add_scaled, resid, has ? delta->data : nullptr, has ? code(delta->dtype) : 0,
+           has ? delta->parts : 0, has ? (long long)delta->part_stride : 0, rows, n_rows, out, hidden, has ? delta->col_scale : nullptr,
+           has ? delta->col_bias : nullptr, s);
+}
+void clamped_glu(const Act &gu, const float *bias, const Act &out, float limit, float slope, float up_shift, cudaStream_t s) {
+  LLM_CALL("elementwise", llm_clamped_glu, code(gu.dtype), code(out.dtype), gu.data, (long long)gu.ld, bias, out.data, (int)gu.rows,
+           (int)out.cols, limit, slope, up_shift, s);
 }
 LLM_KERNEL("elementwise", llm_concat_stream, const float *, const float *, int, long long, const float *, void *, int, int, int,
            cudaStream_t)
 void concat_stream(const float *resid, const Act *delta, const float *other, const Act &out, int hidden, cudaStream_t s) {
+  if (delta && (delta->col_scale || delta->col_bias))
+    LLM_THROW(Unsupported, "concat_stream: a pending addition with a scale or a bias over its columns is taken by the RMS norm's pass only");
   const bool has = delta && delta->data;
   if (has && delta->dtype != DType::F32) LLM_THROW(InvalidArg, "concat_stream: a pending addition is 32-bit");
   LLM_CALL("elementwise", llm_concat_stream, resid, has ? (const float *)delta->data : nullptr, has ? delta->parts : 0,
@@ -304,9 +318,19 @@ void kv_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, in
            write_cache ? 1 : 0, s);
 }
 
+LLM_KERNEL("rope", llm_rope_pairs_place, int, int, const void *, long long, void *, long long, int, int, int, int, int, const float *, int,
+           const float *, int, int, const int *, const int *, const int *, int, void *, void *, int, int, cudaStream_t)
+void rope_pairs_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, int dv, const float *bias, bool values_from_keys,
+                      const float *table, int table_rows, int rot_dim, const int *tok_seq, const int *tok_pos, const int *page_table,
+                      int pt_stride, void *kcache, void *vcache, int page_size, bool write_cache, cudaStream_t s) {
+  LLM_CALL("rope", llm_rope_pairs_place, code(qkv.dtype), code(q_out.dtype), qkv.data, (long long)qkv.ld, q_out.data, (long long)q_out.ld,
+           (int)qkv.rows, n_heads, n_kv, d, dv, bias, values_from_keys ? 1 : 0, table, table_rows, rot_dim, tok_seq, tok_pos, page_table,
+           pt_stride, kcache, vcache, page_size, write_cache ? 1 : 0, s);
+}
+
 // ---------------------------------------------------------------- attention
-LLM_KERNEL("attention_generic", llm_attention_generic, int, const void *, long long, void *, long long, const void *, const void *,
-           const int *, const int *, const int *, int, int, int, int, int, int, int, int, int, int, float, const float *, long long,
+LLM_KERNEL("attention_generic", llm_attention_generic_ld, int, const void *, long long, void *, long long, const void *, const void *,
+           const int *, const int *, const int *, int, int, int, int, int, int, int, int, int, int, int, float, const float *, long long,
            cudaStream_t)
 LLM_KERNEL("attention_decode", llm_attention_decode_sink, const void *, long long, void *, long long, const void *, const void *,
            const int *, const int *, int, int, int, int, int, int, int, int, int, int, int, float, float *, float *, const float *,
@@ -326,10 +350,36 @@ LLM_KERNEL("attention_prefill_tc", llm_attention_prefill_tc, const void *, long 
 
 void attention_generic(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_seq, const int *tok_pos,
                        const int *page_table, int pt_stride, int n_heads, int n_kv, int d, int dv, int page_size, int window,
-                       int block, float scale, const float *gate, long long gate_stride, cudaStream_t s, int sink) {
-  LLM_CALL("attention_generic", llm_attention_generic, code(q.dtype), q.data, (long long)q.ld, out.data, (long long)out.ld, kc, vc,
-           tok_seq, tok_pos, page_table, pt_stride, (int)q.rows, n_heads, n_kv, d, dv, page_size, window, block, sink, scale, gate,
-           gate_stride, s);
+                       int block, float scale, const float *gate, long long gate_stride, cudaStream_t s, int sink, int v_ld) {
+  LLM_CALL("attention_generic", llm_attention_generic_ld, code(q.dtype), q.data, (long long)q.ld, out.data, (long long)out.ld, kc, vc,
+           tok_seq, tok_pos, page_table, pt_stride, (int)q.rows, n_heads, n_kv, d, dv, v_ld > 0 ? v_ld : dv, page_size, window, block,
+           sink, scale, gate, gate_stride, s);
+}
+
+// ---------------------------------------------------------------- latent attention
+LLM_KERNEL("latent", llm_latent_place, int, const float *, long long, int, int, int, const float *, void *, long long, int, int, int,
+           const float *, float, const float *, int, int, const int *, const int *, const int *, int, void *, int, cudaStream_t)
+LLM_KERNEL("latent", llm_latent_absorb, int, const float *, long long, const void *, void *, long long, int, int, int, int, int,
+           const float *, int, int, const int *, cudaStream_t)
+LLM_KERNEL("latent", llm_latent_expand, int, const void *, long long, const void *, void *, long long, int, int, int, int, cudaStream_t)
+void latent_place(const Act &proj, int off_q, int q_rank, const float *q_weight, const Act &cq_out, int off_kv, int kv_rank, int rot,
+                  const float *kv_weight, float eps, const float *table, int table_rows, bool interleaved, const int *tok_seq,
+                  const int *tok_pos, const int *page_table, int pt_stride, void *cache, int page_size, cudaStream_t s) {
+  if (proj.dtype != DType::F32) LLM_THROW(InvalidArg, "latent_place: the latents' projections are 32-bit");
+  LLM_CALL("latent", llm_latent_place, code(cq_out.dtype), (const float *)proj.data, (long long)proj.ld, (int)proj.rows, off_q, q_rank,
+           q_weight, cq_out.data, (long long)cq_out.ld, off_kv, kv_rank, rot, kv_weight, eps, table, table_rows, interleaved ? 1 : 0,
+           tok_seq, tok_pos, page_table, pt_stride, cache, page_size, s);
+}
+void latent_absorb(const Act &q, const void *w_uk, const Act &out, int n_heads, int d, int rot, int kv_rank, const float *table,
+                   int table_rows, bool interleaved, const int *tok_pos, cudaStream_t s) {
+  if (q.dtype != DType::F32) LLM_THROW(InvalidArg, "latent_absorb: the queries are 32-bit");
+  LLM_CALL("latent", llm_latent_absorb, code(out.dtype), (const float *)q.data, (long long)q.ld, w_uk, out.data, (long long)out.ld,
+           (int)q.rows, n_heads, d, rot, kv_rank, table, table_rows, interleaved ? 1 : 0, tok_pos, s);
+}
+void latent_expand(const Act &x, const void *w_uv, const Act &out, int n_heads, int kv_rank, int dv, cudaStream_t s) {
+  if (x.dtype != out.dtype) LLM_THROW(InvalidArg, "latent_expand: input and output have one type");
+  LLM_CALL("latent", llm_latent_expand, code(x.dtype), x.data, (long long)x.ld, w_uv, out.data, (long long)out.ld, (int)x.rows, n_heads,
+           kv_rank, dv, s);
 }
 bool attention_decode_supported(int d, int group) {
   static auto f = resolve<int (*)(int, int)>("attention_decode", "llm_attention_decode_supports");
@@ -443,18 +493,35 @@ void moe_grouped(const Act &x, const void *up, const void *down, const int *offs
 }
 
 // ---------------------------------------------------------------- state carried from token to token
-LLM_KERNEL("recurrent", llm_causal_conv, int, const void *, long long, void *, long long, const float *, void *, const int *,
-           const int *, const int *, const int *, const int *, int, int, int, int, int, cudaStream_t)
+LLM_KERNEL("recurrent", llm_causal_conv_mode, int, const void *, long long, void *, long long, const float *, void *, const int *,
+           const int *, const int *, const int *, const int *, int, int, int, int, int, int, cudaStream_t)
+LLM_KERNEL("recurrent", llm_delta_scan, const float *, long long, int, int, int, const float *, float *, float *, long long, const int *,
+           const int *, int, int, int, int, int, cudaStream_t)
+LLM_KERNEL("recurrent", llm_channel_delta_prepare, float *, long long, const float *, long long, int, int, int, int, int, const float *,
+           const float *, const float *, const float *, float, float *, float *, int, int, int, int, int, cudaStream_t)
 LLM_KERNEL("recurrent", llm_delta_rule, const float *, long long, int, int, int, int, int, int, const float *, const float *,
            const float *, float, float, float *, float *, float *, long long, const int *, const int *, int, int, int, int, cudaStream_t)
 LLM_KERNEL("recurrent", llm_head_norm_gate, const float *, long long, const float *, const float *, long long, float, int, int, int,
            void *, int, long long, cudaStream_t)
 void causal_conv(const Act &h, const Act &out, const float *weight, void *state, const int *tok_seq, const int *tok_pos,
                  const int *seq_start, const int *seq_past, const int *seq_slot, int n_seqs, int taps, bool single_tokens,
-                 cudaStream_t s) {
+                 cudaStream_t s, bool silu_alone) {
   if (h.dtype != out.dtype) LLM_THROW(InvalidArg, "causal_conv: input and output have one type");
-  LLM_CALL("recurrent", llm_causal_conv, code(h.dtype), h.data, (long long)h.ld, out.data, (long long)out.ld, weight, state, tok_seq,
-           tok_pos, seq_start, seq_past, seq_slot, (int)h.rows, n_seqs, (int)h.cols, taps, single_tokens ? 1 : 0, s);
+  LLM_CALL("recurrent", llm_causal_conv_mode, code(h.dtype), h.data, (long long)h.ld, out.data, (long long)out.ld, weight, state, tok_seq,
+           tok_pos, seq_start, seq_past, seq_slot, (int)h.rows, n_seqs, (int)h.cols, taps, single_tokens ? 1 : 0, silu_alone ? 1 : 0, s);
+}
+void delta_scan(const Act &rows, int off_r, int off_k, int off_v, const float *prep, float *state, const Act &out, const int *seq_start,
+                const int *seq_slot, int n_seqs, int n_heads, int d, int dv, cudaStream_t s) {
+  if (rows.dtype != DType::F32 || out.dtype != DType::F32) LLM_THROW(InvalidArg, "delta_scan: vectors and results are 32-bit");
+  LLM_CALL("recurrent", llm_delta_scan, (const float *)rows.data, (long long)rows.ld, off_r, off_k, off_v, prep, state, (float *)out.data,
+           (long long)out.ld, seq_start, seq_slot, (int)rows.rows, n_seqs, n_heads, d, dv, s);
+}
+void channel_delta_prepare(const Act &cv, const Act &proj, int off_b, int off_a1, int rank_a, int off_g1, int rank_g, const float *a2,
+                           const float *dt_bias, const float *a_log, const float *g2, float key_eps, float *prep, float *gate,
+                           int n_heads, int n_kv, int d, int dv, cudaStream_t s) {
+  if (cv.dtype != DType::F32 || proj.dtype != DType::F32) LLM_THROW(InvalidArg, "channel_delta_prepare: projections are 32-bit");
+  LLM_CALL("recurrent", llm_channel_delta_prepare, (float *)cv.data, (long long)cv.ld, (const float *)proj.data, (long long)proj.ld, off_b,
+           off_a1, rank_a, off_g1, rank_g, a2, dt_bias, a_log, g2, key_eps, prep, gate, (int)proj.rows, n_heads, n_kv, d, dv, s);
 }
 void delta_rule(const Act &proj, int off_r, int off_k, int off_v, int off_a, int off_x1, int rank, const float *w2, const float *w0,
                 const float *a_bias, float decay_scale, float key_eps, float *prep, float *state, const Act &out,

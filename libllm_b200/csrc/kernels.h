@@ -42,6 +42,8 @@ void add_layernorm_conv(float *resid, const Act *delta, const float *weight, con
 // out[i] = resid[rows[i]] + delta's parts at that row (32-bit)
 void gather_rows_add(const float *resid, const Act *delta, const int *rows, int n_rows, float *out, int hidden, cudaStream_t s);
 void swiglu(const Act &gu, void *out, DType out_dtype, cudaStream_t s);
+// gu [T, 2 I] (gate | up), bias [2 I] or null; out [T, I] = g * sigmoid(slope g) * (u + up_shift), g and u bounded by limit
+void clamped_glu(const Act &gu, const float *bias, const Act &out, float limit, float slope, float up_shift, cudaStream_t s);
 // out[t] = [resid[t] + delta's parts at t | other[t]] in out's type, [rows, 2 * hidden]
 void concat_stream(const float *resid, const Act *delta, const float *other, const Act &out, int hidden, cudaStream_t s);
 void scale_rows(float *x, long long n, float scale, cudaStream_t s);
@@ -93,6 +95,11 @@ void qk_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, in
               const int *page_table, int pt_stride, void *kcache, void *vcache, int page_size, bool write_cache, cudaStream_t s);
 // Rows [q | k | v | ...] without a rotation: adds `bias` (one 32-bit value per stacked row; null: none), divides each
 // value head by its root mean square when v_eps >= 0, writes q and appends k, v to the cache.
+// rows [q | k | v] (no v part with values_from_keys: the value cache gets the key as projected); bias over the row's columns
+// or null; rotation of the first rot_dim channels of each q and k head in pairs (2i, 2i + 1), table [positions, rot_dim]
+void rope_pairs_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, int dv, const float *bias, bool values_from_keys,
+                      const float *table, int table_rows, int rot_dim, const int *tok_seq, const int *tok_pos, const int *page_table,
+                      int pt_stride, void *kcache, void *vcache, int page_size, bool write_cache, cudaStream_t s);
 void kv_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, int dv, const float *bias, float v_eps,
               const int *tok_seq, const int *tok_pos, const int *page_table, int pt_stride, void *kcache, void *vcache,
               int page_size, bool write_cache, cudaStream_t s);
@@ -102,7 +109,19 @@ void kv_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, in
 // gate_stride; null: none): the head's result is multiplied by sigmoid(gate).
 void attention_generic(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_seq, const int *tok_pos,
                        const int *page_table, int pt_stride, int n_heads, int n_kv, int d, int dv, int page_size, int window,
-                       int block, float scale, const float *gate, long long gate_stride, cudaStream_t s, int sink = 0);
+                       int block, float scale, const float *gate, long long gate_stride, cudaStream_t s, int sink = 0, int v_ld = 0);
+// v_ld > 0: value rows lie v_ld channels apart (the values are the first dv channels of the key rows when vc is kc).
+// ---- latent attention (csrc/latent.cu): attention over one cached row [c | k_r] per position that every head reads
+// proj rows (32-bit) hold the query latent at off_q and, with off_kv >= 0, the key/value latent and the shared key part;
+// cq_out = rms(query latent) * q_weight; the token's cache row = [rms(first kv_rank) * kv_weight | rotated last rot].
+void latent_place(const Act &proj, int off_q, int q_rank, const float *q_weight, const Act &cq_out, int off_kv, int kv_rank, int rot,
+                  const float *kv_weight, float eps, const float *table, int table_rows, bool interleaved, const int *tok_seq,
+                  const int *tok_pos, const int *page_table, int pt_stride, void *cache, int page_size, cudaStream_t s);
+// q [T, heads * (d + rot)] 32-bit -> out [T, heads * (kv_rank + rot)]: [w_uk_h^T q_h[:d] | rotated q_h[d:]]
+void latent_absorb(const Act &q, const void *w_uk, const Act &out, int n_heads, int d, int rot, int kv_rank, const float *table,
+                   int table_rows, bool interleaved, const int *tok_pos, cudaStream_t s);
+// x [T, heads * kv_rank] -> out [T, heads * dv]: out_h = w_uv_h x_h
+void latent_expand(const Act &x, const void *w_uv, const Act &out, int n_heads, int kv_rank, int dv, cudaStream_t s);
 bool attention_decode_supported(int d, int group);
 void attention_decode(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                       int pt_stride, int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window,
@@ -148,10 +167,19 @@ void moe_tc(const Act &x, const void *up, const void *down, const int *offsets, 
             const float *weight, int n_experts, int top, int width, int ff, int act, bool weight_on_output, void *xs, void *mid,
             float *out, int *status, cudaStream_t s, bool gated = false);
 // ---- state carried from token to token (csrc/recurrent.cu)
-// out = h + conv(h) over time per channel, weight [width, taps] 32-bit; state [slots, taps - 1, width] in h's type
+// out = h + conv(h) over time per channel, weight [width, taps] 32-bit; state [slots, taps - 1, width] in h's type.
+// With silu_alone: out = silu(conv(h)), the short convolution of a projection.
 void causal_conv(const Act &h, const Act &out, const float *weight, void *state, const int *tok_seq, const int *tok_pos,
                  const int *seq_start, const int *seq_past, const int *seq_slot, int n_seqs, int taps, bool single_tokens,
-                 cudaStream_t s);
+                 cudaStream_t s, bool silu_alone = false);
+// The delta rule's recurrence alone: rows (32-bit) hold r, k (heads x d) and v (heads x dv) at their offsets, prep
+// [tokens, heads, 3, d] the decay w, the removal b and the direction u; state [slots, heads, dv, d]; out [tokens, heads * dv].
+void delta_scan(const Act &rows, int off_r, int off_k, int off_v, const float *prep, float *state, const Act &out, const int *seq_start,
+                const int *seq_slot, int n_seqs, int n_heads, int d, int dv, cudaStream_t s);
+// The gated delta rule's vectors from the convolved projections (csrc/recurrent.cu says which).
+void channel_delta_prepare(const Act &cv, const Act &proj, int off_b, int off_a1, int rank_a, int off_g1, int rank_g, const float *a2,
+                           const float *dt_bias, const float *a_log, const float *g2, float key_eps, float *prep, float *gate,
+                           int n_heads, int n_kv, int d, int dv, cudaStream_t s);
 // The generalized delta rule over the 32-bit rows `proj` (offsets of r, k, v, the removal logits and the low-rank decay
 // input within a row); prep: scratch [tokens, heads, 3, d] floats; state [slots, heads, d, d] floats; out [tokens, heads * d].
 void delta_rule(const Act &proj, int off_r, int off_k, int off_v, int off_a, int off_x1, int rank, const float *w2, const float *w0,

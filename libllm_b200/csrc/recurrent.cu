@@ -32,12 +32,14 @@ __device__ __forceinline__ float pick(const float (&a)[N], int idx) {
   return r;
 }
 
-// vals[j] = h at position p - taps + 1 + j; the same order of operations wherever a row is computed
-__device__ __forceinline__ float conv_row(const float (&w)[CONV_MAX_TAPS], const float (&vals)[CONV_MAX_TAPS], int taps) {
+// vals[j] = h at position p - taps + 1 + j; the same order of operations wherever a row is computed.
+// mode 0: the input plus its convolution; mode 1: silu of the convolution alone (a projection's short convolution).
+__device__ __forceinline__ float conv_row(const float (&w)[CONV_MAX_TAPS], const float (&vals)[CONV_MAX_TAPS], int taps, int mode) {
   float s = 0.f;
 #pragma unroll
   for (int j = 0; j < CONV_MAX_TAPS; ++j)
     if (j < taps) s = fmaf(w[j], vals[j], s);
+  if (mode == 1) return s / (1.f + expf(-s));
   return pick(vals, taps - 1) + s;
 }
 
@@ -85,7 +87,7 @@ __global__ void __launch_bounds__(CONV_THREADS)
 causal_conv_kernel(const T *__restrict__ h, long long ldh, T *__restrict__ out, long long ldo, const float *__restrict__ weight,
                    T *__restrict__ state, const int *__restrict__ tok_seq, const int *__restrict__ tok_pos,
                    const int *__restrict__ seq_start, const int *__restrict__ seq_past, const int *__restrict__ seq_slot,
-                   int n_tokens, int width, int taps, int n_chunks, int chunk_rows) {
+                   int n_tokens, int width, int taps, int n_chunks, int chunk_rows, int mode) {
   using Vec = ConvVec<T, V>;
   grid_dependents_launch();
   const int c = (blockIdx.x * CONV_THREADS + threadIdx.x) * V;
@@ -105,7 +107,7 @@ causal_conv_kernel(const T *__restrict__ h, long long ldh, T *__restrict__ out, 
       float column[CONV_MAX_TAPS];
 #pragma unroll
       for (int j = 0; j < CONV_MAX_TAPS; ++j) column[j] = vals[j].x[v];
-      r.x[v] = conv_row(w[v], column, taps);
+      r.x[v] = conv_row(w[v], column, taps, mode);
     }
     return r;
   };
@@ -148,11 +150,12 @@ causal_conv_kernel(const T *__restrict__ h, long long ldh, T *__restrict__ out, 
   for (int i = 0; i < keep; ++i) conv_store<T, V>(st + (size_t)i * width, at(n - keep + i));
 }
 
-LLM_EXPORT int llm_causal_conv(int dtype, const void *h, long long ldh, void *out, long long ldo, const float *weight, void *state,
-                               const int *tok_seq, const int *tok_pos, const int *seq_start, const int *seq_past,
-                               const int *seq_slot, int n_tokens, int n_seqs, int width, int taps, int single_tokens,
-                               cudaStream_t stream) {
+LLM_EXPORT int llm_causal_conv_mode(int dtype, const void *h, long long ldh, void *out, long long ldo, const float *weight, void *state,
+                                    const int *tok_seq, const int *tok_pos, const int *seq_start, const int *seq_past,
+                                    const int *seq_slot, int n_tokens, int n_seqs, int width, int taps, int single_tokens, int mode,
+                                    cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(mode == 0 || mode == 1, "causal_conv: mode %d is not known (0: input plus convolution, 1: silu of the convolution)", mode);
   LLM_REQUIRE(n_tokens > 0 && n_seqs > 0 && width > 0, "causal_conv: bad sizes");
   LLM_REQUIRE(taps >= 1 && taps <= CONV_MAX_TAPS, "causal_conv: %d taps are not supported (1 to %d)", taps, CONV_MAX_TAPS);
   LLM_REQUIRE(taps == 1 || state != nullptr, "causal_conv: a convolution of %d taps needs its state", taps);
@@ -170,7 +173,7 @@ LLM_EXPORT int llm_causal_conv(int dtype, const void *h, long long ldh, void *ou
   const dim3 grid((width + CONV_THREADS * v - 1) / (CONV_THREADS * v), n_chunks + n_own);
 #define CONV_GO(T, V)                                                                                                       \
   llm_launch(causal_conv_kernel<T, V>, grid, dim3(CONV_THREADS), 0, stream, (const T *)h, ldh, (T *)out, ldo, weight, (T *)state, \
-             tok_seq, tok_pos, seq_start, seq_past, seq_slot, n_tokens, width, taps, n_chunks, chunk_rows)
+             tok_seq, tok_pos, seq_start, seq_past, seq_slot, n_tokens, width, taps, n_chunks, chunk_rows, mode)
   if (dtype == LLM_F32 && vec) CONV_GO(float, 4);
   else if (dtype == LLM_F32) CONV_GO(float, 1);
   else if (dtype == LLM_BF16 && vec) CONV_GO(__nv_bfloat16, 8);
@@ -179,6 +182,14 @@ LLM_EXPORT int llm_causal_conv(int dtype, const void *h, long long ldh, void *ou
 #undef CONV_GO
   LLM_CHECK_LAUNCH("causal_conv");
   return LLM_OK;
+}
+
+LLM_EXPORT int llm_causal_conv(int dtype, const void *h, long long ldh, void *out, long long ldo, const float *weight, void *state,
+                               const int *tok_seq, const int *tok_pos, const int *seq_start, const int *seq_past,
+                               const int *seq_slot, int n_tokens, int n_seqs, int width, int taps, int single_tokens,
+                               cudaStream_t stream) {
+  return llm_causal_conv_mode(dtype, h, ldh, out, ldo, weight, state, tok_seq, tok_pos, seq_start, seq_past, seq_slot, n_tokens, n_seqs,
+                              width, taps, single_tokens, 0, stream);
 }
 
 // ---------------------------------------------------------------- the delta rule: what each token brings
@@ -339,7 +350,7 @@ template <int DMAX, int LANES, bool VEC>
 __global__ void __launch_bounds__(DR_THREADS + 32)
 delta_rule_kernel(const float *__restrict__ proj, long long ld, int off_r, int off_k, int off_v,
                   const float *__restrict__ prep, float *__restrict__ state, float *__restrict__ out, long long ldo,
-                  const int *__restrict__ seq_start, const int *__restrict__ seq_slot, int n_heads, int d) {
+                  const int *__restrict__ seq_start, const int *__restrict__ seq_slot, int n_heads, int d, int dv) {
   constexpr int ROWS = DMAX / LANES;                 // rows of a column held by one thread
   constexpr int COLS = DR_THREADS / LANES;           // columns of a CTA
   constexpr int PAD = ROWS + 4;                      // a lane's share of a vector, padded: the lanes' loads fall on different banks
@@ -370,7 +381,7 @@ delta_rule_kernel(const float *__restrict__ proj, long long ld, int off_r, int o
     // its row of the product, marked by bit 30) and where to (element i of a vector lies at (i / ROWS) * PAD + i % ROWS).
     const int lane = tid - DR_THREADS;
     int from[PER], to[PER];
-    const int per_vec = d / UNIT, n_v = (min(COLS, d - j0) + UNIT - 1) / UNIT;
+    const int per_vec = d / UNIT, n_v = (min(COLS, dv - j0) + UNIT - 1) / UNIT;
 #pragma unroll
     for (int e = 0; e < PER; ++e) {
       const int idx = lane + e * 32;
@@ -381,7 +392,7 @@ delta_rule_kernel(const float *__restrict__ proj, long long ld, int off_r, int o
         to[e] = which * VLEN + (i / ROWS) * PAD + i % ROWS;
       } else if (idx - 5 * per_vec < n_v) {
         const int i = (idx - 5 * per_vec) * UNIT;
-        from[e] = (off_v + hd * d + j0 + i) | (1 << 30);
+        from[e] = (off_v + hd * dv + j0 + i) | (1 << 30);
         to[e] = 5 * VLEN + i;
       }
     }
@@ -413,15 +424,15 @@ delta_rule_kernel(const float *__restrict__ proj, long long ld, int off_r, int o
   // -------------------------------------------------------------- the two warps of the recurrence
   const int sub = tid % LANES, col = tid / LANES;
   const int j = j0 + col;
-  const bool live = j < d;
+  const bool live = j < dv;
   float S[ROWS];
-  float *sp = state + (((size_t)seq_slot[b] * n_heads + hd) * d + (live ? j : 0)) * d + sub * ROWS;
+  float *sp = state + (((size_t)seq_slot[b] * n_heads + hd) * dv + (live ? j : 0)) * d + sub * ROWS;
 #pragma unroll
   for (int i = 0; i < ROWS; ++i) S[i] = (live && sub * ROWS + i < d) ? sp[i] : 0.f;
   auto token = [&](int t) {
     const float *slot = ring[t % DR_STAGES];
     const float acc = delta_token<ROWS, LANES>(S, slot + sub * PAD, VLEN, slot[5 * VLEN + col]);
-    if (live && sub == 0) out[(size_t)(start + t) * ldo + (size_t)hd * d + j] = acc;
+    if (live && sub == 0) out[(size_t)(start + t) * ldo + (size_t)hd * dv + j] = acc;
   };
   for (int p = 0; p < n_groups; ++p) {
     __syncthreads();
@@ -439,6 +450,34 @@ delta_rule_kernel(const float *__restrict__ proj, long long ld, int off_r, int o
 #pragma unroll
     for (int i = 0; i < ROWS; ++i)
       if (sub * ROWS + i < d) sp[i] = S[i];
+}
+
+static int launch_delta_scan(const float *proj, long long ld, int off_r, int off_k, int off_v, const float *prep, float *state,
+                             float *out, long long ldo, const int *seq_start, const int *seq_slot, int n_seqs, int n_heads, int d,
+                             int dv, cudaStream_t stream) {
+  // 16-byte copies where every vector starts on such a boundary
+  const bool vec16 = d % 4 == 0 && dv % 4 == 0 && ld % 4 == 0 && off_r % 4 == 0 && off_k % 4 == 0 && off_v % 4 == 0 && (uintptr_t)proj % 16 == 0 &&
+                     (uintptr_t)prep % 16 == 0;
+  // Launched without the overlap attribute: the kernel before it (the preparation) is wide and short, this one narrow and
+  // long; let in beside it, its CTAs took their places on the SMs early and a prompt step of 2,048 tokens took 9.8 ms
+  // instead of 5.9 (measured).
+#define DR_GO2(DMAX, LANES, VEC)                                                                                        \
+  llm_launch_after(delta_rule_kernel<DMAX, LANES, VEC>, dim3(n_seqs, n_heads, (dv + DR_THREADS / LANES - 1) / (DR_THREADS / LANES)), \
+                   dim3(DR_THREADS + 32), 0, stream, proj, ld, off_r, off_k, off_v, (const float *)prep, state, out, ldo, seq_start, \
+                   seq_slot, n_heads, d, dv)
+#define DR_GO(DMAX, LANES)              \
+  do {                                  \
+    if (vec16) DR_GO2(DMAX, LANES, true); \
+    else DR_GO2(DMAX, LANES, false);    \
+  } while (0)
+  if (d <= 32) DR_GO(32, 2);
+  else if (d <= 64) DR_GO(64, 4);
+  else if (d <= 128) DR_GO(128, 4);
+  else DR_GO(256, 8);
+#undef DR_GO2
+#undef DR_GO
+  LLM_CHECK_LAUNCH("delta_rule");
+  return LLM_OK;
 }
 
 LLM_EXPORT int llm_delta_rule(const float *proj, long long ld, int off_r, int off_k, int off_v, int off_a, int off_x1, int rank,
@@ -459,29 +498,19 @@ LLM_EXPORT int llm_delta_rule(const float *proj, long long ld, int off_r, int of
                proj, ld, off_k, off_a, off_x1, rank, w2, w0, a_bias, decay_scale, key_eps, n_tokens, n_heads, d, w2_shared, prep);
     LLM_CHECK_LAUNCH("delta_prepare");
   }
-  // 16-byte copies where every vector starts on such a boundary
-  const bool vec16 = d % 4 == 0 && ld % 4 == 0 && off_r % 4 == 0 && off_k % 4 == 0 && off_v % 4 == 0 && (uintptr_t)proj % 16 == 0 &&
-                     (uintptr_t)prep % 16 == 0;
-  // Launched without the overlap attribute: the kernel before it (the preparation) is wide and short, this one narrow and
-  // long; let in beside it, its CTAs took their places on the SMs early and a prompt step of 2,048 tokens took 9.8 ms
-  // instead of 5.9 (measured).
-#define DR_GO2(DMAX, LANES, VEC)                                                                                        \
-  llm_launch_after(delta_rule_kernel<DMAX, LANES, VEC>, dim3(n_seqs, n_heads, (d + DR_THREADS / LANES - 1) / (DR_THREADS / LANES)), \
-                   dim3(DR_THREADS + 32), 0, stream, proj, ld, off_r, off_k, off_v, (const float *)prep, state, out, ldo, seq_start, \
-                   seq_slot, n_heads, d)
-#define DR_GO(DMAX, LANES)              \
-  do {                                  \
-    if (vec16) DR_GO2(DMAX, LANES, true); \
-    else DR_GO2(DMAX, LANES, false);    \
-  } while (0)
-  if (d <= 32) DR_GO(32, 2);
-  else if (d <= 64) DR_GO(64, 4);
-  else if (d <= 128) DR_GO(128, 4);
-  else DR_GO(256, 8);
-#undef DR_GO2
-#undef DR_GO
-  LLM_CHECK_LAUNCH("delta_rule");
-  return LLM_OK;
+  return launch_delta_scan(proj, ld, off_r, off_k, off_v, prep, state, out, ldo, seq_start, seq_slot, n_seqs, n_heads, d, d, stream);
+}
+
+// The recurrence alone, for a mixer that prepares the tokens' vectors itself: rows `proj` (32-bit) hold r and k
+// (heads x d each) and v (heads x dv), `prep` [tokens, heads, 3, d] holds w, b, u; state [slots, heads, dv, d].
+LLM_EXPORT int llm_delta_scan(const float *proj, long long ld, int off_r, int off_k, int off_v, const float *prep, float *state,
+                              float *out, long long ldo, const int *seq_start, const int *seq_slot, int n_tokens, int n_seqs,
+                              int n_heads, int d, int dv, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && n_seqs > 0 && n_heads > 0 && d > 0 && dv > 0, "delta_scan: bad sizes");
+  LLM_REQUIRE(d <= 256, "delta_scan: heads of %d key channels are not supported (up to 256)", d);
+  LLM_REQUIRE(n_heads <= 65535 && n_seqs < 2147483647, "delta_scan: too many heads or sequences");
+  return launch_delta_scan(proj, ld, off_r, off_k, off_v, prep, state, out, ldo, seq_start, seq_slot, n_seqs, n_heads, d, dv, stream);
 }
 
 // ---------------------------------------------------------------- the delta rule: a step of single tokens
@@ -684,5 +713,91 @@ LLM_EXPORT int llm_head_norm_gate(const float *x, long long ldx, const float *we
   else LLM_FAIL("head_norm_gate: unknown dtype %d", out_dtype);
 #undef HNG_GO
   LLM_CHECK_LAUNCH("head_norm_gate");
+  return LLM_OK;
+}
+
+// ---------------------------------------------------------------- the gated delta rule with a decay per key channel
+// Per head, state S [d keys x dv values], in this order:
+//   S <- diag(g) S;  e = beta (v - S^T k);  S <- S + k e^T;  o = S^T q.
+// With w = g, u = g * k (so that u^T S_old = k^T diag(g) S_old), b = beta k and the key that is learned beta k, this is
+//   S <- diag(w) S - b (u^T S) + (beta k) v^T     (both terms read the old S),
+// the recurrence of delta_rule_kernel.  This kernel makes a token's vectors from the convolved projections:
+//   rows `cv` (32-bit) [q (kv_heads x d) | k (kv_heads x d) | v (heads x dv) | room for r (heads x d) | room for k (heads x d)],
+//   q and k made unit vectors per kv head (x / sqrt(sum x^2 + key_eps)), q also times d^(-1/2); head h reads kv head
+//   h / (heads / kv_heads);  beta = sigmoid(proj[off_b + h]);
+//   g = exp(-exp(a_log[h]) * softplus(a2 x1 + dt_bias)), x1 = proj[off_a1 ...] (rank_a values), a2 [heads * d, rank_a];
+//   prep [tokens, heads, 3, d] = w, b, u;  r and beta k into their room of the row;
+//   gate [tokens, heads * dv] = g2 x2, x2 = proj[off_g1 ...] (rank_g values), g2 [heads * dv, rank_g]  (logits; the sigmoid is the
+//   norm kernel's).
+// One CTA a token; sums in lane order then the shuffle tree, whatever the batch.
+constexpr int CD_THREADS = 256;
+__device__ __forceinline__ float softplus32(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+__global__ void __launch_bounds__(CD_THREADS)
+channel_delta_prepare_kernel(float *__restrict__ cv, long long ldc, const float *__restrict__ proj, long long ld, int off_b, int off_a1,
+                             int rank_a, int off_g1, int rank_g, const float *__restrict__ a2, const float *__restrict__ dt_bias,
+                             const float *__restrict__ a_log, const float *__restrict__ g2, float key_eps, float *__restrict__ prep,
+                             float *__restrict__ gate, int n_heads, int n_kv, int d, int dv) {
+  extern __shared__ float cd_sm[];                     // x1 [rank_a] | x2 [rank_g] | inv_q [n_kv] | inv_k [n_kv]
+  float *x1 = cd_sm, *x2 = x1 + rank_a, *inv_q = x2 + rank_g, *inv_k = inv_q + n_kv;
+  grid_dependents_launch();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  float *row = cv + (size_t)t * ldc;
+  const float *pr = proj + (size_t)t * ld;
+  for (int i = threadIdx.x; i < rank_a; i += CD_THREADS) x1[i] = pr[off_a1 + i];
+  for (int i = threadIdx.x; i < rank_g; i += CD_THREADS) x2[i] = pr[off_g1 + i];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int item = warp; item < 2 * n_kv; item += CD_THREADS / 32) {       // q heads, then k heads
+    const float *x = row + (size_t)item * d;
+    float ss = 0.f;
+    for (int c = lane; c < d; c += 32) ss = fmaf(x[c], x[c], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) {
+      if (item < n_kv) inv_q[item] = rsqrtf(ss + key_eps) * rsqrtf((float)d);
+      else inv_k[item - n_kv] = rsqrtf(ss + key_eps);
+    }
+  }
+  __syncthreads();
+  const int group = n_heads / n_kv;
+  const int off_v = 2 * n_kv * d, off_r = off_v + n_heads * dv, off_k = off_r + n_heads * d;
+  for (int i = threadIdx.x; i < n_heads * d; i += CD_THREADS) {
+    const int h = i / d, c = i - h * d, g = h / group;
+    const float q = row[g * d + c] * inv_q[g];
+    const float k = row[(n_kv + g) * d + c] * inv_k[g];
+    const float beta = 1.f / (1.f + expf(-pr[off_b + h]));
+    const float *a = a2 + (size_t)i * rank_a;
+    float s = 0.f;
+    for (int j = 0; j < rank_a; ++j) s = fmaf(a[j], x1[j], s);
+    const float w = expf(-expf(a_log[h]) * softplus32(s + dt_bias[i]));
+    float *p = prep + ((size_t)t * n_heads + h) * 3 * d;
+    p[c] = w;
+    p[d + c] = beta * k;
+    p[2 * d + c] = w * k;
+    row[off_r + i] = q;
+    row[off_k + i] = beta * k;
+  }
+  for (int i = threadIdx.x; i < n_heads * dv; i += CD_THREADS) {
+    const float *a = g2 + (size_t)i * rank_g;
+    float s = 0.f;
+    for (int j = 0; j < rank_g; ++j) s = fmaf(a[j], x2[j], s);
+    gate[(size_t)t * n_heads * dv + i] = s;
+  }
+}
+
+LLM_EXPORT int llm_channel_delta_prepare(float *cv, long long ldc, const float *proj, long long ld, int off_b, int off_a1, int rank_a,
+                                         int off_g1, int rank_g, const float *a2, const float *dt_bias, const float *a_log,
+                                         const float *g2, float key_eps, float *prep, float *gate, int n_tokens, int n_heads, int n_kv,
+                                         int d, int dv, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0 && d > 0 && dv > 0 && rank_a > 0 && rank_g > 0,
+              "channel_delta_prepare: bad sizes");
+  LLM_REQUIRE(ldc >= 2LL * n_kv * d + (long long)n_heads * dv + 2LL * n_heads * d, "channel_delta_prepare: rows too short");
+  const size_t smem = (size_t)(rank_a + rank_g + 2 * n_kv) * sizeof(float);
+  LLM_REQUIRE(smem <= 96 * 1024, "channel_delta_prepare: low-rank inputs of %d and %d values are not supported", rank_a, rank_g);
+  LLM_CHECK_CUDA(llm_allow_smem(channel_delta_prepare_kernel, smem), "channel_delta_prepare attribute");
+  llm_launch(channel_delta_prepare_kernel, dim3(n_tokens), dim3(CD_THREADS), smem, stream, cv, ldc, proj, ld, off_b, off_a1, rank_a, off_g1,
+             rank_g, a2, dt_bias, a_log, g2, key_eps, prep, gate, n_heads, n_kv, d, dv);
+  LLM_CHECK_LAUNCH("channel_delta_prepare");
   return LLM_OK;
 }

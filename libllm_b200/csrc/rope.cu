@@ -480,3 +480,94 @@ LLM_EXPORT int llm_kv_place(int in_dtype, int dtype, const void *qkv, long long 
   LLM_CHECK_LAUNCH("kv_place");
   return LLM_OK;
 }
+
+// ---------------------------------------------------------------- rotation in neighbouring pairs, bias, values from keys
+// Rows [q: n_heads * d | k: n_kv * d | v: n_kv * dv] of a stacked product.  `bias` (32-bit, one value per
+// column of the row; null: none) is added first, in 32-bit.  The first rot_dim channels of every q and k
+// head are rotated in pairs (2i, 2i + 1) by the angle of pair i, whose cosine is table[p][i] and whose
+// sine is table[p][rot_dim/2 + i]:  (u, v) -> (u cos - v sin, v cos + u sin); the other channels pass.
+// q goes to q_out, k to the token's row of the paged key cache.  With values_from_keys the rows have no v
+// part and the value cache gets the key as projected (bias added, not rotated), so dv = d; otherwise v is
+// copied.  One CTA a token, two neighbouring channels to a thread at a time.
+template <typename TI, typename T>
+__global__ void __launch_bounds__(256)
+rope_pairs_place_kernel(const TI *__restrict__ qkv, long long row_stride, T *__restrict__ q_out, long long q_stride, int n_heads,
+                        int n_kv, int d, int dv, const float *__restrict__ bias, int values_from_keys,
+                        const float *__restrict__ table, int table_rows, int rot_dim, const int *__restrict__ tok_seq,
+                        const int *__restrict__ tok_pos, const int *__restrict__ page_table, int pt_stride, T *__restrict__ kcache,
+                        T *__restrict__ vcache, int page_size, int write_cache) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  const TI *row = qkv + (size_t)t * row_stride;
+  const int pos = tok_pos[t];
+  size_t cache_row = 0;
+  if (write_cache) {
+    const int page = page_table[(size_t)tok_seq[t] * pt_stride + pos / page_size];
+    cache_row = (size_t)page * n_kv * page_size + (pos % page_size);
+  }
+  const int half = rot_dim / 2;
+  const float *cs = rot_dim > 0 ? table + (size_t)(pos < table_rows ? pos : table_rows - 1) * rot_dim : nullptr;
+  const int units = (d + 1) / 2;                     // two channels each; the last one may hold a single channel
+  const int n_slots = n_heads + (write_cache ? n_kv : 0);
+  for (int item = threadIdx.x; item < n_slots * units; item += 256) {
+    const int slot = item / units, u = item - slot * units;
+    const int c0 = 2 * u, col = slot * d + c0;
+    const bool two = c0 + 1 < d;
+    const float a = to_float(row[col]) + (bias ? bias[col] : 0.f);
+    const float b = two ? to_float(row[col + 1]) + (bias ? bias[col + 1] : 0.f) : 0.f;
+    float ra = a, rb = b;
+    if (c0 + 1 < rot_dim) {
+      const float c = cs[u], sn = cs[half + u];
+      ra = a * c - b * sn;
+      rb = b * c + a * sn;
+    }
+    if (slot < n_heads) {
+      T *dst = q_out + (size_t)t * q_stride + col;
+      dst[0] = from_float<T>(ra);
+      if (two) dst[1] = from_float<T>(rb);
+    } else {
+      const int kvh = slot - n_heads;
+      T *dst = kcache + (cache_row + (size_t)kvh * page_size) * d + c0;
+      dst[0] = from_float<T>(ra);
+      if (two) dst[1] = from_float<T>(rb);
+      if (values_from_keys) {
+        T *vd = vcache + (cache_row + (size_t)kvh * page_size) * d + c0;
+        vd[0] = from_float<T>(a);
+        if (two) vd[1] = from_float<T>(b);
+      }
+    }
+  }
+  if (write_cache && !values_from_keys) {
+    const int v0 = (n_heads + n_kv) * d;
+    for (int c = threadIdx.x; c < n_kv * dv; c += 256) {
+      const int kvh = c / dv, ch = c - kvh * dv;
+      vcache[(cache_row + (size_t)kvh * page_size) * dv + ch] = from_float<T>(to_float(row[v0 + c]) + (bias ? bias[v0 + c] : 0.f));
+    }
+  }
+}
+
+LLM_EXPORT int llm_rope_pairs_place(int in_dtype, int dtype, const void *qkv, long long row_stride, void *q_out, long long q_stride,
+                                    int n_tokens, int n_heads, int n_kv, int d, int dv, const float *bias, int values_from_keys,
+                                    const float *table, int table_rows, int rot_dim, const int *tok_seq, const int *tok_pos,
+                                    const int *page_table, int pt_stride, void *kcache, void *vcache, int page_size, int write_cache,
+                                    cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && d > 0 && dv > 0, "rope_pairs_place: bad sizes");
+  LLM_REQUIRE(rot_dim >= 0 && rot_dim % 2 == 0 && rot_dim <= d && (rot_dim == 0 || (table != nullptr && table_rows > 0)),
+              "rope_pairs_place: rotated width %d does not fit head size %d", rot_dim, d);
+  LLM_REQUIRE(!values_from_keys || dv == d, "rope_pairs_place: values that are the keys have the keys' width");
+  LLM_REQUIRE(row_stride >= (long long)(n_heads + n_kv) * d + (values_from_keys ? 0LL : (long long)n_kv * dv),
+              "rope_pairs_place: the stacked rows are too short");
+#define PAIRS_PLACE(TI, T)                                                                                               \
+  llm_launch(rope_pairs_place_kernel<TI, T>, dim3(n_tokens), dim3(256), 0, stream, (const TI *)qkv, row_stride, (T *)q_out, q_stride, \
+             n_heads, n_kv, d, dv, bias, values_from_keys, table, table_rows, rot_dim, tok_seq, tok_pos, page_table, pt_stride, \
+             (T *)kcache, (T *)vcache, page_size, write_cache)
+  if (in_dtype == LLM_F32 && dtype == LLM_F32) PAIRS_PLACE(float, float);
+  else if (in_dtype == LLM_F32 && dtype == LLM_BF16) PAIRS_PLACE(float, __nv_bfloat16);
+  else if (in_dtype == LLM_BF16 && dtype == LLM_BF16) PAIRS_PLACE(__nv_bfloat16, __nv_bfloat16);
+  else LLM_FAIL("rope_pairs_place: unsupported dtypes in %d out %d", in_dtype, dtype);
+#undef PAIRS_PLACE
+  LLM_CHECK_LAUNCH("rope_pairs_place");
+  return LLM_OK;
+}

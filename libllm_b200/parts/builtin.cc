@@ -121,7 +121,22 @@ std::vector<double> rotary_frequencies(int64_t rotary_dim, double theta, const J
   if (scaling.is_null()) return freqs;
   ConfigReader r(scaling, "rope description: scaling");
   const std::string type = r.string_or("rope_type", "llama3");
-  if (type != "llama3") LLM_THROW(Config, "rope scaling '%s' is not supported", type.c_str());
+  if (type == "yarn") {
+    // Frequencies whose wavelength is short against the original length stay, long ones are divided by
+    // `factor`, with a linear ramp over the pair index between the pairs that turn beta_fast and beta_slow
+    // times within the original length: pair(t) = d ln(original / (2 pi t)) / (2 ln theta).
+    const double orig = r.number("original_max_position_embeddings"), factor = r.number("factor");
+    const double fast = r.number("beta_fast"), slow = r.number("beta_slow");
+    r.number_or("magnitude", 1.0);                       // on the table's cosines and sines; applied where the table is made
+    auto pair_of = [&](double turns) { return (double)rotary_dim * std::log(orig / (2.0 * M_PI * turns)) / (2.0 * std::log(theta)); };
+    const double lo = std::max(std::floor(pair_of(fast)), 0.0), hi = std::min(std::ceil(pair_of(slow)), (double)rotary_dim - 1.0);
+    for (size_t i = 0; i < freqs.size(); ++i) {
+      const double ramp = std::min(std::max(((double)i - lo) / std::max(hi - lo, 0.001), 0.0), 1.0);
+      freqs[i] = freqs[i] / factor * ramp + freqs[i] * (1.0 - ramp);
+    }
+    return freqs;
+  }
+  if (type != "llama3") LLM_THROW(Config, "rope scaling '%s' is not supported (llama3, yarn)", type.c_str());
   const double orig = (double)r.integer("original_max_position_embeddings");
   const double lo = r.number("low_freq_factor"), hi = r.number("high_freq_factor"), factor = r.number("factor");
   for (auto &f : freqs) {
@@ -150,6 +165,11 @@ class RotaryEmbedding : public PositionEncoding {
     head_dim_ = r.integer("head_dim");
     rotary_dim_ = r.integer_or("rotary_dim", head_dim_);
     theta_ = r.number_or("theta", 10000.0);
+    const std::string pairing = r.string_or("pairing", "half");
+    if (pairing != "half" && pairing != "interleaved") r.fail("'pairing' must be \"half\" (channel i with i + rotary_dim/2) or \"interleaved\" (2i with 2i + 1)");
+    interleaved_ = pairing == "interleaved";
+    const Json &sc = spec.get("scaling");
+    if (sc.is_object() && sc.has("magnitude") && sc.get("magnitude").is_number()) magnitude_ = sc.get("magnitude").as_number();
     if (rotary_dim_ % 2 || rotary_dim_ > head_dim_ || rotary_dim_ <= 0)
       LLM_THROW(Config, "rotary width %lld does not fit head size %lld", (long long)rotary_dim_, (long long)head_dim_);
     rotary_frequencies(rotary_dim_, theta_, spec.get("scaling"));     // checks the scaling's keys
@@ -170,8 +190,8 @@ class RotaryEmbedding : public PositionEncoding {
     for (int64_t p = 0; p < P; ++p)
       for (int64_t i = 0; i < half; ++i) {
         const double a = (double)p * freqs[(size_t)i];
-        host[(size_t)(p * rotary_dim_ + i)] = (float)std::cos(a);
-        host[(size_t)(p * rotary_dim_ + half + i)] = (float)std::sin(a);
+        host[(size_t)(p * rotary_dim_ + i)] = (float)(std::cos(a) * magnitude_);
+        host[(size_t)(p * rotary_dim_ + half + i)] = (float)(std::sin(a) * magnitude_);
       }
     table_ = std::make_shared<Weight>();
     table_->dtype = DType::F32;
@@ -182,20 +202,34 @@ class RotaryEmbedding : public PositionEncoding {
     if (env_.shared) (*env_.shared)[key] = table_;
   }
   void rotate_and_store(StepContext &ctx, const Act &qkv, const Act &q_out, const QkvLayout &l, LayerCache &cache) override {
+    if (interleaved_) {
+      kernels::rope_pairs_place(qkv, q_out, l.n_heads, l.n_kv_heads, l.head_dim, l.head_dim, nullptr, false, table_->buf.as<float>(),
+                                (int)table_->rows, (int)rotary_dim_, ctx.tok_seq, ctx.tok_pos, cache.page_table, cache.table_width,
+                                cache.k, cache.v, cache.page_size, cache.writes, ctx.stream);
+      return;
+    }
     kernels::rope_cache_write(qkv, q_out, l.n_heads, l.n_kv_heads, l.head_dim, table_->buf.as<float>(), (int)table_->rows,
                               (int)rotary_dim_, ctx.tok_seq, ctx.tok_pos, cache.page_table, cache.table_width, cache.k, cache.v,
                               cache.page_size, cache.writes, ctx.stream);
   }
   const float *half_split_table(int *rows, int *rotary_dim) const override {
+    if (!table_ || interleaved_) return nullptr;
+    *rows = (int)table_->rows;
+    *rotary_dim = (int)rotary_dim_;
+    return table_->buf.as<float>();
+  }
+  const float *pair_table(int *rows, int *rotary_dim, bool *interleaved) const override {
     if (!table_) return nullptr;
     *rows = (int)table_->rows;
     *rotary_dim = (int)rotary_dim_;
+    *interleaved = interleaved_;
     return table_->buf.as<float>();
   }
 
  private:
   int64_t head_dim_, rotary_dim_;
-  double theta_;
+  double theta_, magnitude_ = 1.0;
+  bool interleaved_ = false;
   std::shared_ptr<Weight> table_;
 };
 
@@ -219,6 +253,9 @@ class RotaryEmbedding : public PositionEncoding {
 //                (at their true positions); the cache holds on to their pages
 //   v_norm       {eps}: every value head is divided by its root mean square over its channels before it
 //                is cached (no weight)
+//   values       "keys": there is no value matrix; a position's value is its key as projected (bias added), before
+//                the rotation.  Needs a rotation in neighbouring pairs (position.pairing "interleaved"), whose
+//                placement kernel also adds the biases (32-bit)
 //   q_bias, k_bias, v_bias   names of the biases (default: the matrix's name with "weight" replaced by "bias").
 //                Without a rotation the biases are added where q, k and v are placed (32-bit), so that the
 //                product itself runs on the tensor cores like any other
@@ -235,7 +272,8 @@ class Attention : public Mixer {
     scale_ = (float)r.number_or("scale", 1.0 / std::sqrt((double)d_), false);
     q_name_ = r.string("q");
     k_name_ = r.string("k");
-    v_name_ = r.string("v");
+    values_from_keys_ = r.string_or("values", "own") == "keys";
+    v_name_ = values_from_keys_ ? std::string() : r.string("v");
     o_name_ = r.string("o");
     if (n_heads_ % n_kv_) LLM_THROW(Config, "attention: %d heads are not a multiple of %d groups", n_heads_, n_kv_);
     dv_ = (int)r.integer_or("v_head_dim", d_);
@@ -258,14 +296,19 @@ class Attention : public Mixer {
     if (sink_ > 0 && (window_ == 0 || block_ > 0)) LLM_THROW(Config, "attention: kept first positions ('sink') go with a window");
     if (r.present("v_norm")) v_eps_ = (float)ConfigReader(r.object("v_norm"), "attention description: v_norm").number("eps", false);
     if (!spec.get("position").is_null()) position_ = build_as<PositionEncoding>("position", spec.get("position"), env);
-    place_adds_bias_ = !position_ && q_norm_name_.empty();
+    const Json &pos_spec = spec.get("position");
+    pairs_place_ = position_ && pos_spec.is_object() && pos_spec.has("pairing") && pos_spec.get("pairing").is_string() &&
+                   pos_spec.get("pairing").as_string() == "interleaved" && q_norm_name_.empty();
+    place_adds_bias_ = (!position_ && q_norm_name_.empty()) || pairs_place_;
+    if (values_from_keys_ && (!pairs_place_ || dv_ != d_ || !gate_name_.empty() || v_eps_ >= 0.f))
+      LLM_THROW(Unsupported, "attention: values that are the keys go with a rotation in neighbouring pairs, values as wide as keys, no gate and no value norm");
     if (v_eps_ >= 0.f && !place_adds_bias_) LLM_THROW(Unsupported, "attention: a value norm together with a rotation or a q/k norm is not built");
     if (bias_ && !place_adds_bias_ && (!gate_name_.empty() || !q_norm_name_.empty()))
       LLM_THROW(Unsupported, "attention: a bias together with a rotation and a gate or a q/k norm is not built");
     for (const char *key : {"q_bias", "k_bias", "v_bias"}) bias_names_.push_back(r.string_or(key, ""));
     q_width_ = (int64_t)n_heads_ * d_;
     kv_width_ = (int64_t)n_kv_ * d_;
-    v_width_ = (int64_t)n_kv_ * dv_;
+    v_width_ = values_from_keys_ ? 0 : (int64_t)n_kv_ * dv_;
     o_width_ = (int64_t)n_heads_ * dv_;
     gate_offset_ = q_width_ + kv_width_ + v_width_;
     // rows of the stacked matrix: a multiple of 8, so that rows of the 32-bit product start on 32 bytes
@@ -276,11 +319,13 @@ class Attention : public Mixer {
   }
 
   std::vector<TensorNeed> tensor_needs() const override {
-    std::vector<TensorNeed> needs = {{q_name_, {q_width_, hidden_}}, {k_name_, {kv_width_, hidden_}}, {v_name_, {v_width_, hidden_}},
-                                     {o_name_, {hidden_, o_width_}}};
+    std::vector<TensorNeed> needs = {{q_name_, {q_width_, hidden_}}, {k_name_, {kv_width_, hidden_}}};
+    if (!values_from_keys_) needs.push_back({v_name_, {v_width_, hidden_}});
+    needs.push_back({o_name_, {hidden_, o_width_}});
     if (bias_) {
       size_t which = 0;
       for (const auto &p : {std::make_pair(q_name_, q_width_), std::make_pair(k_name_, kv_width_), std::make_pair(v_name_, v_width_)}) {
+        if (p.first.empty()) continue;                 // no value matrix
         std::string n = p.first;
         const std::string suffix = "weight";
         if (n.size() >= suffix.size() && n.compare(n.size() - suffix.size(), suffix.size(), suffix) == 0) n.resize(n.size() - suffix.size());
@@ -309,9 +354,11 @@ class Attention : public Mixer {
     char *p = (char *)w_qkv_.buf.get();
     l.fetch_into(needs[0], l.engine, p);
     l.fetch_into(needs[1], l.engine, p + (size_t)q_width_ * hidden_ * es);
-    l.fetch_into(needs[2], l.engine, p + (size_t)(q_width_ + kv_width_) * hidden_ * es);
-    w_o_ = l.fetch(needs[3]);
-    size_t next = bias_ ? 7 : 4;
+    const size_t nv = values_from_keys_ ? 0 : 1;      // matrices and biases of the values
+    if (nv) l.fetch_into(needs[2], l.engine, p + (size_t)(q_width_ + kv_width_) * hidden_ * es);
+    w_o_ = l.fetch(needs[2 + nv]);
+    const size_t first_bias = 3 + nv;
+    size_t next = bias_ ? first_bias + 2 + nv : first_bias;
     if (!q_norm_name_.empty()) {
       q_norm_ = l.fetch(needs[next]);
       k_norm_ = l.fetch(needs[next + 1]);
@@ -324,9 +371,9 @@ class Attention : public Mixer {
       b_qkv_.cols = w_qkv_.rows;
       b_qkv_.buf.allocate((size_t)w_qkv_.rows * 4, true);
       float *b = b_qkv_.buf.as<float>();
-      l.fetch_into(needs[4], DType::F32, b);
-      l.fetch_into(needs[5], DType::F32, b + q_width_);
-      l.fetch_into(needs[6], DType::F32, b + q_width_ + kv_width_);
+      l.fetch_into(needs[first_bias], DType::F32, b);
+      l.fetch_into(needs[first_bias + 1], DType::F32, b + q_width_);
+      if (nv) l.fetch_into(needs[first_bias + 2], DType::F32, b + q_width_ + kv_width_);
       if (l.engine == DType::BF16 && !place_adds_bias_) {
         static bool said = false;
         if (!said) {
@@ -414,7 +461,15 @@ class Attention : public Mixer {
     Act q = ctx.arena->act(ctx.dtype, ctx.n_tokens, q_width_);
     const QkvLayout layout{n_heads_, n_kv_, d_};
     if (has_gate) gate = (const float *)qkv.data + gate_offset_;
-    if (place_adds_bias_ && (bias_ || v_eps_ >= 0.f)) {
+    if (pairs_place_) {
+      int rows = 0, rot = 0;
+      bool interleaved = false;
+      const float *pairs = position_->pair_table(&rows, &rot, &interleaved);
+      if (!pairs || !interleaved) LLM_THROW(Unsupported, "attention: the position part has no table of neighbouring pairs");
+      kernels::rope_pairs_place(qkv, q, n_heads_, n_kv_, d_, dv_, bias_ ? b_qkv_.buf.as<float>() : nullptr, values_from_keys_, pairs, rows,
+                                rot, ctx.tok_seq, ctx.tok_pos, cache->page_table, cache->table_width, cache->k, cache->v,
+                                cache->page_size, cache->writes, ctx.stream);
+    } else if (place_adds_bias_ && (bias_ || v_eps_ >= 0.f)) {
       kernels::kv_place(qkv, q, n_heads_, n_kv_, d_, dv_, bias_ ? b_qkv_.buf.as<float>() : nullptr, v_eps_, ctx.tok_seq, ctx.tok_pos,
                         cache->page_table, cache->table_width, cache->k, cache->v, cache->page_size, cache->writes, ctx.stream);
     } else if (!q_norm_name_.empty() || dv_ != d_) {
@@ -484,7 +539,7 @@ class Attention : public Mixer {
   int64_t hidden_, q_width_, kv_width_, v_width_, o_width_, gate_offset_, stacked_rows_;
   int64_t gate_rows_ = 0;
   int n_heads_, n_kv_, d_, dv_, window_, block_, sink_ = 0;
-  bool bias_, plain_, gate_per_channel_ = false, place_adds_bias_ = false;
+  bool bias_, plain_, gate_per_channel_ = false, place_adds_bias_ = false, values_from_keys_ = false, pairs_place_ = false;
   float scale_, qk_eps_ = 0.f, v_eps_ = -1.f;
   std::vector<std::string> bias_names_;
   std::string q_name_, k_name_, v_name_, o_name_, q_norm_name_, k_norm_name_, gate_name_;
@@ -563,6 +618,8 @@ class SwiGLU : public FeedForward {
 //               token itself, zeros before the sequence's start); the last taps - 1 rows of n are
 //               state of the run, per sequence, in the engine's type
 //   ff, ff_norm may be null: the block is the mixer alone
+//   mixer_scale, ff_scale  names of vectors [hidden]: a sublayer's result is multiplied by its vector,
+//               channel by channel, before it is added to the stream (32-bit, in the pass that adds it)
 const char *const CONV_STATE = "mixer_conv.inputs";
 class PreNormBlock : public Block {
  public:
@@ -581,6 +638,9 @@ class PreNormBlock : public Block {
       hidden_ = c.integer("hidden");
       if (taps_ > 8) LLM_THROW(Unsupported, "prenorm block: a convolution of %d taps is not supported (up to 8)", taps_);
     }
+    mixer_scale_name_ = r.string_or("mixer_scale", "");
+    ff_scale_name_ = ff_ ? r.string_or("ff_scale", "") : "";
+    if (!mixer_scale_name_.empty() || !ff_scale_name_.empty()) hidden_ = r.integer("hidden");
   }
   std::vector<Part *> parts() const {
     std::vector<Part *> p = {mixer_norm_.get(), mixer_.get()};
@@ -602,11 +662,15 @@ class PreNormBlock : public Block {
     for (Part *p : parts())
       for (auto &n : p->tensor_needs()) out.push_back(n);
     if (taps_ > 0) out.push_back({conv_name_, {hidden_, (int64_t)taps_}, TensorRole::Vector, false});
+    if (!mixer_scale_name_.empty()) out.push_back({mixer_scale_name_, {hidden_}, TensorRole::Vector, false});
+    if (!ff_scale_name_.empty()) out.push_back({ff_scale_name_, {hidden_}, TensorRole::Vector, false});
     return out;
   }
   void load(const Loader &l) override {
     for (Part *p : parts()) p->load(l);
     if (taps_ > 0) conv_ = l.fetch({conv_name_, {hidden_, (int64_t)taps_}, TensorRole::Vector, false});
+    if (!mixer_scale_name_.empty()) mixer_scale_ = l.fetch({mixer_scale_name_, {hidden_}, TensorRole::Vector, false});
+    if (!ff_scale_name_.empty()) ff_scale_ = l.fetch({ff_scale_name_, {hidden_}, TensorRole::Vector, false});
   }
   std::vector<std::string> kernel_families() const override {
     std::vector<std::string> out;
@@ -655,10 +719,13 @@ class PreNormBlock : public Block {
     } else {
       h = mixer_norm_->forward(ctx, stream);
     }
-    sink(true);
+    // a result that is scaled before it is added cannot be added by the product that makes it
+    const float *mixer_scale = mixer_scale_name_.empty() ? nullptr : mixer_scale_.buf.as<float>();
+    const float *ff_scale = ff_scale_name_.empty() ? nullptr : ff_scale_.buf.as<float>();
+    sink(mixer_scale == nullptr);
     Act r = mixer_->forward(ctx, h, cache, state);
     sink(false);
-    stream.pending = r.data == (void *)stream.resid ? Act() : r;
+    stream.pending = r.data == (void *)stream.resid ? Act() : scaled(r, mixer_scale);
     if (ctx.nothing_read_after) {       // no logits wanted from this step: the stream is read by nobody
       flush_chain(ctx);
       stream.pending = Act();
@@ -678,20 +745,26 @@ class PreNormBlock : public Block {
       stream.picked = true;
     }
     h = ff_norm_->forward(ctx, stream);
-    sink(true);
+    sink(ff_scale == nullptr);
     r = ff_->forward(ctx, h);
     sink(false);
-    stream.pending = r.data == (void *)stream.resid ? Act() : r;
+    stream.pending = r.data == (void *)stream.resid ? Act() : scaled(r, ff_scale);
   }
 
  private:
+  static Act scaled(Act r, const float *scale) {
+    if (!scale) return r;
+    if (r.col_scale) LLM_THROW(Unsupported, "prenorm block: a sublayer's result carries a scale of its own beside the block's");
+    r.col_scale = scale;
+    return r;
+  }
   std::unique_ptr<Norm> mixer_norm_, ff_norm_;
   std::unique_ptr<Mixer> mixer_;
   std::unique_ptr<FeedForward> ff_;
   int taps_ = 0;
   int64_t hidden_ = 0;
-  std::string conv_name_;
-  Weight conv_;
+  std::string conv_name_, mixer_scale_name_, ff_scale_name_;
+  Weight conv_, mixer_scale_, ff_scale_;
 };
 
 // ---------------------------------------------------------------- parallel block
@@ -827,11 +900,13 @@ void register_part_raw(const std::string &category, const std::string &kind, Par
 
 void register_feed_forward_parts();   // parts/feed_forward.cc
 void register_recurrent_parts();      // parts/recurrent.cc
+void register_latent_parts();         // parts/latent.cc
 
 void register_builtin_parts() {
   register_part_raw("block", "parallel", factory_of<ParallelBlock>());
   register_feed_forward_parts();
   register_recurrent_parts();
+  register_latent_parts();
   register_part_raw("norm", "rmsnorm", factory_of<RMSNorm>());
   register_part_raw("norm", "layernorm", factory_of<LayerNorm>());
   register_part_raw("position", "rope", factory_of<RotaryEmbedding>());

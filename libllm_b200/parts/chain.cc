@@ -46,7 +46,7 @@ bool Chain::add_norm(float *resid, const Act *delta, const float *weight, float 
                      int hidden, cudaStream_t stream) {
   const bool has = delta && delta->data;
   if (hidden % 4 != 0 || hidden > kernels::gemm_chain_max_hidden() || n_rows <= 0 || !out) return false;
-  if (has && (delta->dtype != DType::F32 || delta->parts > 8 || delta->part_stride % 4 != 0)) return false;
+  if (has && (delta->dtype != DType::F32 || delta->parts > 8 || delta->part_stride % 4 != 0 || delta->col_scale || delta->col_bias)) return false;
   if ((int)jobs_.size() >= kernels::gemm_chain_max_jobs()) flush(stream);
   kernels::ChainJob job = {};
   job.kind = 2;

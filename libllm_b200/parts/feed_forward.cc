@@ -209,6 +209,88 @@ class RoutedFeedForward : public FeedForward {
   std::unique_ptr<FeedForward> shared_;
 };
 
+// ---------------------------------------------------------------- clamped gated unit
+// down(g * sigmoid(slope g) * (u + up_shift)) with g = min(gate x, limit), u = clamp(up x, -limit, limit).
+// Gate and up are one stacked product with a 32-bit result; their biases (optional) are added where the
+// unit is computed, in 32-bit, so that the product runs on the tensor cores like any other; the down
+// matrix's bias (optional) rides with the result and is added, in 32-bit, by the pass that adds the
+// result to the residual stream (Act::col_bias).  `limit` 0: no bounds.
+class ClampedGlu : public FeedForward {
+ public:
+  ClampedGlu(const Json &spec, const BuildEnv &env) : FeedForward(spec, env) {
+    ConfigReader r(spec, "clamped_glu description");
+    hidden_ = r.integer("hidden");
+    inter_ = r.integer("intermediate");
+    limit_ = (float)r.number_or("limit", 0.0, false);
+    slope_ = (float)r.number_or("slope", 1.0, false);
+    up_shift_ = (float)r.number_or("up_shift", 0.0, false);
+    if (limit_ < 0.f) r.fail("'limit' must not be negative");
+    gate_ = r.string("gate");
+    up_ = r.string("up");
+    down_ = r.string("down");
+    gate_bias_ = r.string_or("gate_bias", "");
+    up_bias_ = r.string_or("up_bias", "");
+    down_bias_ = r.string_or("down_bias", "");
+    if (gate_bias_.empty() != up_bias_.empty()) r.fail("'gate_bias' and 'up_bias' come together");
+  }
+  std::vector<TensorNeed> tensor_needs() const override {
+    std::vector<TensorNeed> needs = {{gate_, {inter_, hidden_}}, {up_, {inter_, hidden_}}, {down_, {hidden_, inter_}}};
+    if (!gate_bias_.empty()) {
+      needs.push_back({gate_bias_, {inter_}, TensorRole::Vector, false});
+      needs.push_back({up_bias_, {inter_}, TensorRole::Vector, false});
+    }
+    if (!down_bias_.empty()) needs.push_back({down_bias_, {hidden_}, TensorRole::Vector, false});
+    return needs;
+  }
+  void load(const Loader &l) override {
+    const auto needs = tensor_needs();
+    const size_t es = dtype_size(l.engine);
+    w_gate_up_.dtype = l.engine;
+    w_gate_up_.rows = 2 * inter_;
+    w_gate_up_.cols = hidden_;
+    w_gate_up_.buf.allocate((size_t)(2 * inter_ * hidden_) * es);
+    l.fetch_into(needs[0], l.engine, w_gate_up_.buf.get());
+    l.fetch_into(needs[1], l.engine, (char *)w_gate_up_.buf.get() + (size_t)(inter_ * hidden_) * es);
+    w_down_ = l.fetch(needs[2]);
+    size_t next = 3;
+    if (!gate_bias_.empty()) {
+      b_gate_up_.dtype = DType::F32;
+      b_gate_up_.rows = 1;
+      b_gate_up_.cols = 2 * inter_;
+      b_gate_up_.buf.allocate((size_t)(2 * inter_) * sizeof(float));
+      l.fetch_into(needs[next], DType::F32, b_gate_up_.buf.get());
+      l.fetch_into(needs[next + 1], DType::F32, b_gate_up_.buf.as<float>() + inter_);
+      next += 2;
+    }
+    if (!down_bias_.empty()) b_down_ = l.fetch(needs[next]);
+  }
+  std::vector<std::string> kernel_families() const override {
+    std::vector<std::string> fams = product_families(env_.dtype);
+    fams.push_back("elementwise");
+    return fams;
+  }
+  Act forward(StepContext &ctx, const Act &x) override {
+    Act gu = linear(ctx, x, w_gate_up_, nullptr, DType::F32);
+    flush_chain(ctx);
+    Act m = ctx.arena->act(ctx.dtype, x.rows, inter_);
+    kernels::clamped_glu(gu, gate_bias_.empty() ? nullptr : b_gate_up_.buf.as<float>(), m, limit_, slope_, up_shift_, ctx.stream);
+    if (down_bias_.empty()) return linear(ctx, m, w_down_, nullptr, DType::F32, true);
+    // with a bias the product cannot add to the stream as it stores: the bias goes with the result
+    float *const sink = ctx.residual_sink;
+    ctx.residual_sink = nullptr;
+    Act y = linear(ctx, m, w_down_, nullptr, DType::F32, true);
+    ctx.residual_sink = sink;
+    y.col_bias = b_down_.buf.as<float>();
+    return y;
+  }
+
+ private:
+  int64_t hidden_, inter_;
+  float limit_, slope_, up_shift_;
+  std::string gate_, up_, down_, gate_bias_, up_bias_, down_bias_;
+  Weight w_gate_up_, w_down_, b_gate_up_, b_down_;
+};
+
 template <typename T>
 PartFactory factory_of() {
   return [](const Json &spec, const BuildEnv &env) { return std::unique_ptr<Part>(new T(spec, env)); };
@@ -221,6 +303,7 @@ void register_part_raw(const std::string &category, const std::string &kind, Par
 void register_feed_forward_parts() {
   register_part_raw("feed_forward", "mlp", factory_of<Mlp>());
   register_part_raw("feed_forward", "moe", factory_of<RoutedFeedForward>());
+  register_part_raw("feed_forward", "clamped_glu", factory_of<ClampedGlu>());
 }
 
 }  // namespace llm

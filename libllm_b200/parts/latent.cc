@@ -1,0 +1,167 @@
+// "latent_attention": attention whose keys and values are functions of one cached vector per position.
+//
+// With h the mixer's input, H heads of `head_dim` unrotated and `rot_dim` rotated query/key channels, values of
+// `v_head_dim`, latents of `q_rank` and `kv_rank` channels:
+//   c_q = rms(W_dq h) * q_norm,   q = W_uq c_q, head by head [head_dim unrotated | rot_dim rotated]
+//   [c' | k_r'] = W_dkv h,        c = rms(c') * kv_norm,   k_r = rotated k_r' (one part that all heads share)
+//   head: k = [W_uk c | k_r], v = W_uv c, score = (q . k) * scale, causal softmax, then W_o on the heads.
+// Only [c | k_r] is cached: one row of kv_rank + rot_dim channels per position (cache need: one key head of
+// that width, no value storage).  The products with W_uk and W_uv are moved to the query's side and behind the
+// weighted sum (csrc/latent.cu says how), so a step reads the cached rows once per head and never expands them.
+// A run that the schedule gives another run's cache (ScheduleEntry::cache_from) has no W_dkv of its own: it
+// reads the rows that run appended, with its own W_uk, W_uv and queries.  The rotation is the position part's
+// (either pairing; its table carries whatever the scaling puts on cosines and sines); `scale` is the
+// description's.  The reference has no such mixer (its attention: src/libllm/llama.cc:178-225).
+#include <cmath>
+
+#include "config/config.h"
+#include "csrc/kernels.h"
+#include "parts/chain.h"
+#include "parts/linear.h"
+#include "parts/part.h"
+
+namespace llm {
+
+namespace {
+
+class LatentAttention : public Mixer {
+ public:
+  LatentAttention(const Json &spec, const BuildEnv &env) : Mixer(spec, env) {
+    ConfigReader r(spec, "latent_attention description");
+    hidden_ = r.integer("hidden");
+    n_heads_ = (int)r.integer("n_heads");
+    d_ = (int)r.integer("head_dim");
+    rot_ = (int)r.integer("rot_dim", 0);
+    dv_ = (int)r.integer_or("v_head_dim", d_);
+    kv_rank_ = (int)r.integer("kv_rank");
+    q_rank_ = (int)r.integer("q_rank");
+    scale_ = (float)r.number_or("scale", 1.0 / std::sqrt((double)(d_ + rot_)), false);
+    eps_ = (float)r.number("eps");
+    q_down_ = r.string("q_down");
+    q_norm_ = r.string("q_norm");
+    q_up_ = r.string("q_up");
+    kv_down_ = r.string_or("kv_down", "");
+    kv_norm_ = r.string_or("kv_norm", "");
+    if (kv_down_.empty() != kv_norm_.empty()) r.fail("'kv_down' and 'kv_norm' come together");
+    k_up_ = r.string("k_up");
+    v_up_ = r.string("v_up");
+    o_ = r.string("o");
+    if (rot_ % 2) r.fail("'rot_dim' must be even");
+    if (kv_rank_ + rot_ > 1024 || kv_rank_ > 1024)
+      LLM_THROW(Unsupported, "latent_attention: cached rows of %d channels are not supported (up to 1024)", kv_rank_ + rot_);
+    if (rot_ > 0) {
+      if (spec.get("position").is_null()) r.fail("rotated channels need a 'position' part");
+      position_ = build_as<PositionEncoding>("position", spec.get("position"), env);
+    }
+    down_rows_ = ((int64_t)q_rank_ + (own_latent() ? kv_rank_ + rot_ : 0) + 7) / 8 * 8;
+  }
+  bool own_latent() const { return !kv_down_.empty(); }
+
+  std::vector<TensorNeed> tensor_needs() const override {
+    std::vector<TensorNeed> needs = {{q_down_, {(int64_t)q_rank_, hidden_}},
+                                     {q_norm_, {(int64_t)q_rank_}, TensorRole::Vector, false},
+                                     {q_up_, {(int64_t)n_heads_ * (d_ + rot_), (int64_t)q_rank_}},
+                                     {k_up_, {(int64_t)n_heads_ * d_, (int64_t)kv_rank_}},
+                                     {v_up_, {(int64_t)n_heads_ * dv_, (int64_t)kv_rank_}},
+                                     {o_, {hidden_, (int64_t)n_heads_ * dv_}}};
+    if (own_latent()) {
+      needs.push_back({kv_down_, {(int64_t)kv_rank_ + rot_, hidden_}});
+      needs.push_back({kv_norm_, {(int64_t)kv_rank_}, TensorRole::Vector, false});
+    }
+    if (position_)
+      for (auto &n : position_->tensor_needs()) needs.push_back(n);
+    return needs;
+  }
+
+  void load(const Loader &l) override {
+    const std::vector<TensorNeed> needs = tensor_needs();
+    const size_t es = dtype_size(l.engine);
+    // both latents' projections are one stacked product [W_dq; W_dkv] with a 32-bit result
+    w_down_.dtype = l.engine;
+    w_down_.rows = down_rows_;
+    w_down_.cols = hidden_;
+    w_down_.buf.allocate((size_t)down_rows_ * (size_t)hidden_ * es, true);
+    l.fetch_into(needs[0], l.engine, w_down_.buf.get());
+    w_q_norm_ = l.fetch(needs[1]);
+    w_uq_ = l.fetch(needs[2]);
+    w_uk_ = l.fetch(needs[3]);
+    w_uv_ = l.fetch(needs[4]);
+    w_o_ = l.fetch(needs[5]);
+    if (own_latent()) {
+      l.fetch_into(needs[6], l.engine, (char *)w_down_.buf.get() + (size_t)q_rank_ * hidden_ * es);
+      w_kv_norm_ = l.fetch(needs[7]);
+    }
+    if (position_) position_->load(l);
+  }
+
+  std::vector<std::string> kernel_families() const override {
+    std::vector<std::string> fams = product_families(env_.dtype);
+    fams.push_back("latent");
+    fams.push_back("attention_generic");
+    return fams;
+  }
+
+  bool wants_cache() const override { return true; }
+  CacheNeed cache_need() const override {
+    CacheNeed n;
+    n.kind = "full";
+    n.n_kv_heads = 1;
+    n.k_dim = kv_rank_ + rot_;
+    n.v_dim = 0;                                       // the values are functions of the key rows
+    return n;
+  }
+
+  Act forward(StepContext &ctx, const Act &x, LayerCache *cache, StateView *) override {
+    if (!cache) LLM_THROW(InvalidArg, "latent_attention: the run has no cache to attend over");
+    if (cache->need.n_kv_heads != 1 || cache->need.k_dim != kv_rank_ + rot_)
+      LLM_THROW(Config, "latent_attention: the cache holds rows of %d x %d channels, this run reads rows of %d", cache->need.n_kv_heads,
+                cache->need.k_dim, kv_rank_ + rot_);
+    if (own_latent() != cache->writes)
+      LLM_THROW(Config, own_latent() ? "latent_attention: a run with a latent projection of its own was given another run's cache"
+                                     : "latent_attention: a run without a latent projection needs another run's cache");
+    int table_rows = 0, rot = 0;
+    bool interleaved = false;
+    const float *table = nullptr;
+    if (position_) {
+      table = position_->pair_table(&table_rows, &rot, &interleaved);
+      if (!table || rot != rot_) LLM_THROW(Unsupported, "latent_attention: the position part has no table of %d rotated channels", rot_);
+    }
+    const int T = ctx.n_tokens;
+    const int row = kv_rank_ + rot_;
+    Act proj = linear(ctx, x, w_down_, nullptr, DType::F32);
+    flush_chain(ctx);
+    Act cq = ctx.arena->act(ctx.dtype, T, q_rank_);
+    kernels::latent_place(proj, 0, q_rank_, w_q_norm_.buf.as<float>(), cq, own_latent() ? q_rank_ : -1, kv_rank_, rot_,
+                          own_latent() ? w_kv_norm_.buf.as<float>() : nullptr, eps_, table, table_rows, interleaved, ctx.tok_seq,
+                          ctx.tok_pos, cache->page_table, cache->table_width, cache->k, cache->page_size, ctx.stream);
+    Act q = linear(ctx, cq, w_uq_, nullptr, DType::F32);
+    flush_chain(ctx);
+    Act qa = ctx.arena->act(ctx.dtype, T, (int64_t)n_heads_ * row);
+    kernels::latent_absorb(q, w_uk_.buf.get(), qa, n_heads_, d_, rot_, kv_rank_, table, table_rows, interleaved, ctx.tok_pos, ctx.stream);
+    Act mixed = ctx.arena->act(ctx.dtype, T, (int64_t)n_heads_ * kv_rank_);
+    kernels::attention_generic(qa, mixed, cache->k, cache->k, ctx.tok_seq, ctx.tok_pos, cache->page_table, cache->table_width, n_heads_, 1,
+                               row, kv_rank_, cache->page_size, 0, 0, scale_, nullptr, 0, ctx.stream, 0, row);
+    Act heads = ctx.arena->act(ctx.dtype, T, (int64_t)n_heads_ * dv_);
+    kernels::latent_expand(mixed, w_uv_.buf.get(), heads, n_heads_, kv_rank_, dv_, ctx.stream);
+    return linear(ctx, heads, w_o_, nullptr, DType::F32, true);
+  }
+
+ private:
+  int64_t hidden_, down_rows_;
+  int n_heads_, d_, rot_, dv_, kv_rank_, q_rank_;
+  float scale_, eps_;
+  std::string q_down_, q_norm_, q_up_, kv_down_, kv_norm_, k_up_, v_up_, o_;
+  std::unique_ptr<PositionEncoding> position_;
+  Weight w_down_, w_q_norm_, w_uq_, w_uk_, w_uv_, w_o_, w_kv_norm_;
+};
+
+}  // namespace
+
+void register_part_raw(const std::string &category, const std::string &kind, PartFactory factory);   // parts/part.cc
+
+void register_latent_parts() {
+  register_part_raw("mixer", "latent_attention",
+                    [](const Json &spec, const BuildEnv &env) { return std::unique_ptr<Part>(new LatentAttention(spec, env)); });
+}
+
+}  // namespace llm

@@ -258,6 +258,15 @@ class PositionEncoding : public Part {
     (void)rotary_dim;
     return nullptr;
   }
+  // The same table for either pairing: row p holds rotary_dim/2 cosines, then as many sines, of the angles
+  // p * f_i (times whatever the scaling puts on both); pair i is channels (i, i + rotary_dim/2), or, with
+  // *interleaved, channels (2i, 2i + 1).  Null: this part has no such table.
+  virtual const float *pair_table(int *rows, int *rotary_dim, bool *interleaved) const {
+    (void)rows;
+    (void)rotary_dim;
+    (void)interleaved;
+    return nullptr;
+  }
 };
 
 class Mixer : public Part {

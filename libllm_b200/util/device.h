@@ -121,6 +121,10 @@ struct Act {
   int64_t rows = 0, cols = 0, ld = 0;
   int parts = 1;
   int64_t part_stride = 0;
+  // For a result that is yet to be added to the residual stream: 32-bit vectors over the columns (device
+  // memory, either may be null); what is added is (sum of parts + col_bias) * col_scale.
+  const float *col_scale = nullptr;
+  const float *col_bias = nullptr;
 };
 
 // A weight on the device: [rows, cols] row-major, or a vector (rows = 1).
