@@ -467,6 +467,114 @@ def run_compare_sesuzen(args):
     return 0
 
 
+# ---------------------------------------------------------------- Sobezen beside Llama at equal sizes
+def sobezen_config(hidden, runs, heads, kv, dim, ff, vocab, kv_rank=512, taps=4, limit=7.0):
+    """A Sobezen model of `runs` layers in the order delta rule, attention (values are the keys), latent attention with
+    rows of its own, latent attention that reads the rows of the layer before it; every layer has the dense gated
+    feed-forward.  The latent layers' heads have `dim` unrotated and dim / 2 rotated channels and a query latent of
+    3 / 8 of the width."""
+    rot = dict(dims=dim, base=1e4)
+    rot_l = dict(dims=dim // 2, base=1e4, scaling=dict(factor=4.0, original=2048, fast=16.0, slow=2.0))
+    mlp = dict(kind="dense", ff=ff, limit=limit)
+    layers = []
+    for i in range(runs):
+        k = i % 4
+        if k == 0:
+            L = dict(type="channel_delta", mixer=dict(heads=hidden // dim, kv_heads=max(1, hidden // dim // 4), dim=dim, vdim=dim, conv=taps))
+        elif k == 1:
+            L = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv, dim=dim, vdim=dim, scale=dim ** -0.5, rot=rot))
+        else:
+            m = dict(heads=heads, dim=dim, rot_dim=dim // 2, vdim=dim, kv_rank=kv_rank, q_rank=hidden * 3 // 8,
+                     scale=(dim + dim // 2) ** -0.5, rot=rot_l)
+            if k == 3:
+                m["kv_from"] = i - 1
+            L = dict(type="latent_attention", mixer=m)
+        layers.append(dict(mlp=mlp, **L))
+    return dict(architecture="Sobezen", vocab=vocab, width=hidden, norm=dict(eps=1e-5), embedding=dict(scale=1.0), logit_scale=1.0,
+                layers=layers)
+
+
+SOBEZEN_FREE_RANK = 16        # the size Model.from_random gives the low-rank inputs' inner side
+
+
+def sobezen_numbers(c):
+    """(bytes a decode step reads apart from the cache, cache bytes per visible token, bytes of recurrent state a step
+    reads and writes per sequence, prefill flops of T tokens with one wanted row)."""
+    H, V = c["width"], c["vocab"]
+    mats, kv_per_token, state_bytes, att_flops_per_key, rec_flops_per_token = 0, 0, 0, 0, 0
+    for L in c["layers"]:
+        m = L["mixer"]
+        if L["type"] == "attention":
+            mats += H * (m["heads"] + m["kv_heads"]) * m["dim"] + m["heads"] * m["dim"] * H
+            kv_per_token += 2 * 2 * m["kv_heads"] * m["dim"]                                  # rotated keys and the keys as values
+            att_flops_per_key += 2 * m["heads"] * 2 * m["dim"]
+        elif L["type"] == "latent_attention":
+            row = m["kv_rank"] + m["rot_dim"]
+            mats += H * m["q_rank"] + m["q_rank"] * m["heads"] * (m["dim"] + m["rot_dim"]) + m["heads"] * (m["dim"] + m["vdim"]) * m["kv_rank"]
+            mats += m["heads"] * m["vdim"] * H + (0 if "kv_from" in m else H * row)
+            kv_per_token += 2 * row                                                           # a borrower reads the rows again
+            att_flops_per_key += 2 * m["heads"] * (row + m["kv_rank"])
+        else:
+            qk, k, v, r = m["kv_heads"] * m["dim"], m["heads"] * m["dim"], m["heads"] * m["vdim"], SOBEZEN_FREE_RANK
+            mats += H * (2 * qk + v + m["heads"] + 2 * r) + v * H + 2 * r * (k + v)             # the second low-rank sides in 32-bit
+            state_bytes += 2 * 4 * m["heads"] * m["dim"] * m["vdim"]
+            rec_flops_per_token += 8 * m["heads"] * m["dim"] * m["vdim"]                       # decay, prediction, write, read-out
+        if L["mlp"]:
+            mats += 3 * H * L["mlp"]["ff"]
+    weight_bytes = 2 * (mats + V * H)
+
+    def prefill_flops(T):
+        return 2 * T * mats + att_flops_per_key * T * (T + 1) // 2 + rec_flops_per_token * T + 2 * V * H
+    return weight_bytes, kv_per_token, state_bytes, prefill_flops
+
+
+SOBEZEN_SIZES = {
+    # name: (hidden, layers, heads, kv heads, head size, feed-forward, vocabulary)
+    "2k": (2048, 8, 32, 8, 64, 8192, 32000),
+    "4k": (4096, 4, 32, 8, 128, 14336, 32000),
+}
+
+
+def run_compare_sobezen(args):
+    """Prefill and decode of Sobezen beside Llama, both with random weights, at equal hidden size, number of layers,
+    heads, head size, feed-forward width (three matrices in both) and vocabulary: one JSON line per size and model."""
+    import torch
+    from libllm_b200 import Model
+    pk = peaks()
+    names = [n for n in SOBEZEN_SIZES if not args.sizes or n in args.sizes.split(",")]
+    for name in names:
+        hidden, runs, heads, kv, dim, ff, vocab = SOBEZEN_SIZES[name]
+        llama = dict(LLAMA_1B, num_hidden_layers=runs, hidden_size=hidden, num_attention_heads=heads, num_key_value_heads=kv,
+                     head_dim=dim, intermediate_size=ff, vocab_size=vocab, tie_word_embeddings=False, rope_scaling=None)
+        zen = sobezen_config(hidden, runs, heads, kv, dim, ff, vocab)
+        for label, cfg in (("llama", llama), ("sobezen", zen)):
+            if args.model and args.model != label:
+                continue
+            state_bytes = 0
+            if label == "llama":
+                wbytes, kv_per_tok, flops_fn = model_numbers(cfg)
+            else:
+                wbytes, kv_per_tok, state_bytes, flops_fn = sobezen_numbers(cfg)
+            flops = flops_fn(PROMPT)
+            model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=args.batch * CONTEXT, max_seq_len=CONTEXT)
+            pre = prefill_rate(model, vocab, lambda T: flops, pk["bf16_tflops"])
+            rate, ms, ctx_len, launches = decode_rate(model, args.batch, args.steps, args.warmup, vocab)
+            step_bytes = wbytes + args.batch * (ctx_len * kv_per_tok + state_bytes)
+            print(json.dumps({"compare": name, "model": label, "batch": args.batch, "prompt": PROMPT,
+                              "config": {"hidden": hidden, "layers": runs, "heads": heads, "kv_heads": kv, "head_dim": dim, "ff": ff,
+                                         "vocab": vocab, "order": [L["type"] for L in zen["layers"]] if label == "sobezen" else None},
+                              "prefill": {"ms": round(pre["ms"], 3), "tok_s": round(pre["value"], 1), "tflop": round(flops / 1e12, 3),
+                                          "frac_of_gemm_peak": round(pre["frac"], 4)},
+                              "decode": {"tok_s": round(rate, 1), "ms_per_step": round(ms, 4), "launches_per_step": launches,
+                                         "step_gb": round(step_bytes / 1e9, 3),
+                                         "hbm_frac": round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)},
+                              "peaks": pk["source"]}), flush=True)
+            model.engine.close()
+            del model
+            torch.cuda.empty_cache()
+    return 0
+
+
 def run_compare(args):
     """Prefill and decode of Sinezen beside Llama, both with random weights, at equal hidden size, layer
     runs, heads, head size, feed-forward width (with experts: equal matrix values used per token) and
@@ -581,9 +689,9 @@ def main():
                     help="1b: the benchmark line (default); 3b, 8b: the larger workloads, a line of their own")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print a short line (for profiling; not a bench record)")
-    ap.add_argument("--compare", choices=["sinezen", "sesuzen"], default=None,
-                    help="Sinezen or Sesuzen beside Llama at equal sizes: prefill and decode, a line per size and model (not a bench record)")
-    ap.add_argument("--model", choices=["llama", "sesuzen"], default=None, help="with --compare sesuzen: one of the two models only")
+    ap.add_argument("--compare", choices=["sinezen", "sesuzen", "sobezen"], default=None,
+                    help="Sinezen, Sesuzen or Sobezen beside Llama at equal sizes: prefill and decode, a line per size and model (not a bench record)")
+    ap.add_argument("--model", choices=["llama", "sesuzen", "sobezen"], default=None, help="with --compare sesuzen or sobezen: one of the two models only")
     ap.add_argument("--sizes", default=None, help="with --compare: which of the sizes (2k, 4k, 2k-routed), with commas")
     ap.add_argument("--prompt-len", type=int, default=None,
                     help="with --only: prompts of this many tokens instead of 2048 (the context grows to fit)")
@@ -603,6 +711,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.compare == "sesuzen":
         return run_compare_sesuzen(args)
+    if args.compare == "sobezen":
+        return run_compare_sobezen(args)
     if args.compare:
         return run_compare(args)
     if args.workload != "1b":
