@@ -283,7 +283,10 @@ LLM_API int32_t llm_part_forward(llm_part_t *p, llm_json_t *call, llm_json_t *re
     } else if (PositionEncoding *pos = dynamic_cast<PositionEncoding *>(h.part.get())) {
       int rows = 0, rot = 0;
       const float *t = pos->half_split_table(&rows, &rot);
+      bool interleaved = false;
+      if (!t) t = pos->pair_table(&rows, &rot, &interleaved);     // a rotation of neighbouring pairs has this table alone
       Json tj = Json::object();
+      tj.set("interleaved", interleaved);
       tj.set("ptr", (int64_t)(uintptr_t)t);
       tj.set("rows", rows);
       tj.set("rotary_dim", rot);

@@ -51,6 +51,7 @@ FAMILIES: Dict[str, dict] = {
     "recurrent": dict(sources=["recurrent.cu"], headers=["common.cuh"]),
     "attention_generic": dict(sources=["attention_generic.cu"], headers=["common.cuh"]),
     "latent": dict(sources=["latent.cu"], headers=["common.cuh"]),
+    "latent_tc": dict(sources=["latent_tc.cu"], headers=["common.cuh", "mma_tiles.cuh"]),
     "sampling": dict(sources=["sampling.cu"], headers=["common.cuh"]),
     "moe": dict(sources=["moe.cu"], headers=["common.cuh", "mma_tiles.cuh"]),
     "moe_tc": dict(sources=["moe_tc.cu"], headers=["common.cuh", "tc_common.cuh"]),

@@ -381,6 +381,51 @@ void latent_expand(const Act &x, const void *w_uv, const Act &out, int n_heads, 
   LLM_CALL("latent", llm_latent_expand, code(x.dtype), x.data, (long long)x.ld, w_uv, out.data, (long long)out.ld, (int)x.rows, n_heads,
            kv_rank, dv, s);
 }
+LLM_KERNEL("latent_tc", llm_latent_rows, const void *, int, int, int, const int *, const int *, const int *, int, int, void *, void *,
+           cudaStream_t)
+LLM_KERNEL("latent_tc", llm_latent_rotate_q, const float *, long long, void *, long long, int, int, int, int, const float *, int, int,
+           const int *, cudaStream_t)
+LLM_KERNEL("latent_tc", llm_latent_prefill, const void *, long long, const void *, long long, const void *, void *, long long, const int *,
+           int, int, int, int, int, int, float, cudaStream_t)
+LLM_KERNEL("latent_tc", llm_latent_decode, const void *, long long, const void *, int, const int *, const int *, const int *, int, int,
+           int, int, int, int, float, void *, long long, float *, cudaStream_t)
+void latent_rows(const void *cache, int page_size, int row, int kv_rank, const int *tok_seq, const int *tok_pos, const int *page_table,
+                 int pt_stride, int n_tokens, const Act &c_out, const Act &kr_out, cudaStream_t s) {
+  if (c_out.dtype != DType::BF16 || c_out.ld != kv_rank || (row > kv_rank && (kr_out.dtype != DType::BF16 || kr_out.ld != row - kv_rank)))
+    LLM_THROW(InvalidArg, "latent_rows: dense bfloat16 results");
+  LLM_CALL("latent_tc", llm_latent_rows, cache, page_size, row, kv_rank, tok_seq, tok_pos, page_table, pt_stride, n_tokens, c_out.data,
+           kr_out.data, s);
+}
+void latent_rotate_q(const Act &q, const Act &out, int n_heads, int d, int rot, const float *table, int table_rows, bool interleaved,
+                     const int *tok_pos, cudaStream_t s) {
+  if (q.dtype != DType::F32 || out.dtype != DType::BF16) LLM_THROW(InvalidArg, "latent_rotate_q: 32-bit queries, a bfloat16 result");
+  LLM_CALL("latent_tc", llm_latent_rotate_q, (const float *)q.data, (long long)q.ld, out.data, (long long)out.ld, (int)q.rows, n_heads, d,
+           rot, table, table_rows, interleaved ? 1 : 0, tok_pos, s);
+}
+bool latent_prefill_supported(int d, int rot, int dv) {
+  static auto f = resolve<int (*)(int, int, int)>("latent_tc", "llm_latent_prefill_supports");
+  return f(d, rot, dv) != 0;
+}
+void latent_prefill(const Act &q, const Act &kv, const Act &kr, const Act &out, const int *seq_start, int n_seqs, int max_q_len,
+                    int n_heads, int d, int rot, int dv, float scale, cudaStream_t s) {
+  if (q.dtype != DType::BF16 || kv.dtype != DType::BF16 || out.dtype != DType::BF16 || (rot > 0 && (kr.dtype != DType::BF16 || kr.ld != rot)))
+    LLM_THROW(InvalidArg, "latent_prefill: bfloat16 operands");
+  LLM_CALL("latent_tc", llm_latent_prefill, q.data, (long long)q.ld, kv.data, (long long)kv.ld, kr.data, out.data, (long long)out.ld,
+           seq_start, n_seqs, max_q_len, n_heads, d, rot, dv, scale, s);
+}
+bool latent_decode_supported(int kv_rank, int rot) {
+  static auto f = resolve<int (*)(int, int)>("latent_tc", "llm_latent_decode_supports");
+  return f(kv_rank, rot) != 0;
+}
+size_t latent_decode_floats(int n_tokens, int n_heads, int kv_rank, int n_splits) {
+  return n_splits <= 1 ? 0 : (size_t)n_tokens * n_heads * n_splits * ((size_t)kv_rank + 2);
+}
+void latent_decode(const Act &qa, const void *cache, int page_size, const int *tok_seq, const int *tok_pos, const int *page_table,
+                   int pt_stride, int n_heads, int kv_rank, int rot, int n_splits, float scale, const Act &out, float *ws, cudaStream_t s) {
+  if (qa.dtype != DType::BF16 || out.dtype != DType::BF16) LLM_THROW(InvalidArg, "latent_decode: bfloat16 operands");
+  LLM_CALL("latent_tc", llm_latent_decode, qa.data, (long long)qa.ld, cache, page_size, tok_seq, tok_pos, page_table, pt_stride,
+           (int)qa.rows, n_heads, kv_rank, rot, n_splits, scale, out.data, (long long)out.ld, ws, s);
+}
 bool attention_decode_supported(int d, int group) {
   static auto f = resolve<int (*)(int, int)>("attention_decode", "llm_attention_decode_supports");
   return f(d, group) != 0;

@@ -122,6 +122,22 @@ void latent_absorb(const Act &q, const void *w_uk, const Act &out, int n_heads, 
                    int table_rows, bool interleaved, const int *tok_pos, cudaStream_t s);
 // x [T, heads * kv_rank] -> out [T, heads * dv]: out_h = w_uv_h x_h
 void latent_expand(const Act &x, const void *w_uv, const Act &out, int n_heads, int kv_rank, int dv, cudaStream_t s);
+// ---- latent attention on the tensor cores (csrc/latent_tc.cu), bfloat16
+// The cached rows of the step's tokens, whoever appended them: c_out [T, kv_rank], kr_out [T, row - kv_rank].
+void latent_rows(const void *cache, int page_size, int row, int kv_rank, const int *tok_seq, const int *tok_pos, const int *page_table,
+                 int pt_stride, int n_tokens, const Act &c_out, const Act &kr_out, cudaStream_t s);
+// q [T, heads * (d + rot)] 32-bit -> out, the same layout in bfloat16 with each head's last rot channels rotated
+void latent_rotate_q(const Act &q, const Act &out, int n_heads, int d, int rot, const float *table, int table_rows, bool interleaved,
+                     const int *tok_pos, cudaStream_t s);
+bool latent_prefill_supported(int d, int rot, int dv);
+// Sequences that start at their first token, heads materialised: kv [T, heads * d | heads * dv], kr [T, rot] rotated.
+void latent_prefill(const Act &q, const Act &kv, const Act &kr, const Act &out, const int *seq_start, int n_seqs, int max_q_len,
+                    int n_heads, int d, int rot, int dv, float scale, cudaStream_t s);
+bool latent_decode_supported(int kv_rank, int rot);
+size_t latent_decode_floats(int n_tokens, int n_heads, int kv_rank, int n_splits);
+// qa [T, heads * (kv_rank + rot)] (latent_absorb) over the cached rows -> out [T, heads * kv_rank]; ws: latent_decode_floats
+void latent_decode(const Act &qa, const void *cache, int page_size, const int *tok_seq, const int *tok_pos, const int *page_table,
+                   int pt_stride, int n_heads, int kv_rank, int rot, int n_splits, float scale, const Act &out, float *ws, cudaStream_t s);
 bool attention_decode_supported(int d, int group);
 void attention_decode(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                       int pt_stride, int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window,

@@ -12,6 +12,7 @@
 // reads the rows that run appended, with its own W_uk, W_uv and queries.  The rotation is the position part's
 // (either pairing; its table carries whatever the scaling puts on cosines and sines); `scale` is the
 // description's.  The reference has no such mixer (its attention: src/libllm/llama.cc:178-225).
+#include <algorithm>
 #include <cmath>
 
 #include "config/config.h"
@@ -87,6 +88,16 @@ class LatentAttention : public Mixer {
     w_uk_ = l.fetch(needs[3]);
     w_uv_ = l.fetch(needs[4]);
     w_o_ = l.fetch(needs[5]);
+    if (l.engine == DType::BF16) {
+      // [W_uk; W_uv] stacked, for prompt steps that materialise the heads' keys and values in one product
+      const int64_t k_rows = (int64_t)n_heads_ * d_, v_rows = (int64_t)n_heads_ * dv_;
+      w_ukv_.dtype = l.engine;
+      w_ukv_.rows = (k_rows + v_rows + 7) / 8 * 8;
+      w_ukv_.cols = kv_rank_;
+      w_ukv_.buf.allocate((size_t)w_ukv_.rows * (size_t)kv_rank_ * es, true);
+      l.fetch_into(needs[3], l.engine, w_ukv_.buf.get());
+      l.fetch_into(needs[4], l.engine, (char *)w_ukv_.buf.get() + (size_t)k_rows * kv_rank_ * es);
+    }
     if (own_latent()) {
       l.fetch_into(needs[6], l.engine, (char *)w_down_.buf.get() + (size_t)q_rank_ * hidden_ * es);
       w_kv_norm_ = l.fetch(needs[7]);
@@ -97,6 +108,7 @@ class LatentAttention : public Mixer {
   std::vector<std::string> kernel_families() const override {
     std::vector<std::string> fams = product_families(env_.dtype);
     fams.push_back("latent");
+    if (env_.dtype == DType::BF16) fams.push_back("latent_tc");
     fams.push_back("attention_generic");
     return fams;
   }
@@ -134,14 +146,47 @@ class LatentAttention : public Mixer {
     kernels::latent_place(proj, 0, q_rank_, w_q_norm_.buf.as<float>(), cq, own_latent() ? q_rank_ : -1, kv_rank_, rot_,
                           own_latent() ? w_kv_norm_.buf.as<float>() : nullptr, eps_, table, table_rows, interleaved, ctx.tok_seq,
                           ctx.tok_pos, cache->page_table, cache->table_width, cache->k, cache->page_size, ctx.stream);
+    const bool tc = ctx.dtype == DType::BF16 && kernels::available("latent_tc");
+    bool from_start = !ctx.decode_only && !ctx.captured && (int)ctx.past_lens.size() == ctx.n_seqs;
+    for (int past : ctx.past_lens) from_start = from_start && past == 0;
+    Act heads = ctx.arena->act(ctx.dtype, T, (int64_t)n_heads_ * dv_);
+    if (tc && from_start && w_ukv_.buf.get() && kernels::latent_prefill_supported(d_, rot_, dv_)) {
+      // every sequence brings its first tokens: the heads' keys and values of the step's own rows are one product
+      // over the rows as the cache holds them, and the attention is the flash form over those
+      Act c = ctx.arena->act(ctx.dtype, T, kv_rank_);
+      Act kr = ctx.arena->act(ctx.dtype, T, std::max(rot_, 8));
+      kr.cols = kr.ld = rot_;
+      kernels::latent_rows(cache->k, cache->page_size, row, kv_rank_, ctx.tok_seq, ctx.tok_pos, cache->page_table, cache->table_width, T,
+                           c, kr, ctx.stream);
+      Act q = linear(ctx, cq, w_uq_, nullptr, DType::F32);
+      Act kv = linear(ctx, c, w_ukv_, nullptr, ctx.dtype);
+      flush_chain(ctx);
+      Act qb = ctx.arena->act(ctx.dtype, T, (int64_t)n_heads_ * (d_ + rot_));
+      kernels::latent_rotate_q(q, qb, n_heads_, d_, rot_, table, table_rows, interleaved, ctx.tok_pos, ctx.stream);
+      kernels::latent_prefill(qb, kv, kr, heads, ctx.seq_start, ctx.n_seqs, ctx.max_q_len, n_heads_, d_, rot_, dv_, scale_, ctx.stream);
+      return linear(ctx, heads, w_o_, nullptr, DType::F32, true);
+    }
     Act q = linear(ctx, cq, w_uq_, nullptr, DType::F32);
     flush_chain(ctx);
     Act qa = ctx.arena->act(ctx.dtype, T, (int64_t)n_heads_ * row);
     kernels::latent_absorb(q, w_uk_.buf.get(), qa, n_heads_, d_, rot_, kv_rank_, table, table_rows, interleaved, ctx.tok_pos, ctx.stream);
     Act mixed = ctx.arena->act(ctx.dtype, T, (int64_t)n_heads_ * kv_rank_);
-    kernels::attention_generic(qa, mixed, cache->k, cache->k, ctx.tok_seq, ctx.tok_pos, cache->page_table, cache->table_width, n_heads_, 1,
-                               row, kv_rank_, cache->page_size, 0, 0, scale_, nullptr, 0, ctx.stream, 0, row);
-    Act heads = ctx.arena->act(ctx.dtype, T, (int64_t)n_heads_ * dv_);
+    if (tc && kernels::latent_decode_supported(kv_rank_, rot_)) {
+      // all heads of a token over the cached rows; long sequences in runs of at least two tiles of keys, enough
+      // of them to fill the device twice; the same for every step of a captured graph
+      const int max_len = std::max(ctx.max_kv_len, 1);
+      const int ctas = std::max(1, T * ((n_heads_ + 31) / 32));
+      const int want = std::max(1, (2 * ctx.sm_count + ctas - 1) / ctas);
+      const int most = std::max(1, max_len / 128);
+      const int n_splits = std::max(1, std::min(std::min(want, most), 64));
+      float *ws = nullptr;
+      if (n_splits > 1) ws = ctx.arena->alloc_n<float>(kernels::latent_decode_floats(T, n_heads_, kv_rank_, n_splits));
+      kernels::latent_decode(qa, cache->k, cache->page_size, ctx.tok_seq, ctx.tok_pos, cache->page_table, cache->table_width, n_heads_,
+                             kv_rank_, rot_, n_splits, scale_, mixed, ws, ctx.stream);
+    } else {
+      kernels::attention_generic(qa, mixed, cache->k, cache->k, ctx.tok_seq, ctx.tok_pos, cache->page_table, cache->table_width, n_heads_,
+                                 1, row, kv_rank_, cache->page_size, 0, 0, scale_, nullptr, 0, ctx.stream, 0, row);
+    }
     kernels::latent_expand(mixed, w_uv_.buf.get(), heads, n_heads_, kv_rank_, dv_, ctx.stream);
     return linear(ctx, heads, w_o_, nullptr, DType::F32, true);
   }
@@ -152,7 +197,7 @@ class LatentAttention : public Mixer {
   float scale_, eps_;
   std::string q_down_, q_norm_, q_up_, kv_down_, kv_norm_, k_up_, v_up_, o_;
   std::unique_ptr<PositionEncoding> position_;
-  Weight w_down_, w_q_norm_, w_uq_, w_uk_, w_uv_, w_o_, w_kv_norm_;
+  Weight w_down_, w_q_norm_, w_uq_, w_uk_, w_uv_, w_ukv_, w_o_, w_kv_norm_;
 };
 
 }  // namespace
