@@ -15,6 +15,7 @@
 // 32-bit: norms (sums over the product's 32-bit result), rotation, every accumulation.
 #include "common.cuh"
 #include <math.h>
+#include <algorithm>
 
 LLM_DEFINE_LAST_ERROR(llm_latent_last_error)
 
@@ -97,7 +98,8 @@ LLM_EXPORT int llm_latent_place(int dtype, const float *proj, long long ld, int 
 // ---------------------------------------------------------------- the queries take in W_uk
 // q rows (32-bit) [heads, d + rot]: out[t, h] = [sum_i q[t, h, i] * w_uk[h * d + i, :] (kv_rank) | rotated q[t, h, d:] (rot)]
 // in the engine's type.  A CTA takes one head and TT tokens: the tokens' unrotated parts lie in shared memory, a
-// thread owns output channels and walks the head's d rows of w_uk (its neighbours read the neighbouring channels).
+// thread owns output channels and walks the head's d rows of w_uk (its neighbours read the neighbouring channels);
+// the channels are shared out over blockIdx.z so that a step of few tokens still fills the device.
 constexpr int LAT_TT = 16;
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS)
@@ -115,10 +117,11 @@ latent_absorb_kernel(const float *__restrict__ q, long long ldq, const T *__rest
   }
   __syncthreads();
   const T *w = w_uk + (size_t)h * d * kv_rank;
-  for (int c = threadIdx.x; c < kv_rank; c += THREADS) {
+  for (int c = blockIdx.z * THREADS + threadIdx.x; c < kv_rank; c += THREADS * gridDim.z) {
     float acc[LAT_TT];
 #pragma unroll
     for (int t = 0; t < LAT_TT; ++t) acc[t] = 0.f;
+#pragma unroll 4
     for (int i = 0; i < d; ++i) {
       const float wv = to_float(w[(size_t)i * kv_rank + c]);
 #pragma unroll
@@ -129,6 +132,7 @@ latent_absorb_kernel(const float *__restrict__ q, long long ldq, const T *__rest
       if (t < nt) out[(size_t)(t0 + t) * ldo + (size_t)h * (kv_rank + rot) + c] = from_float<T>(acc[t]);
   }
   const int half = rot / 2;
+  if (blockIdx.z != 0) return;
   for (int i = threadIdx.x; i < nt * half; i += THREADS) {
     const int t = i / half, pr = i - t * half;
     const int pos = tok_pos[t0 + t];
@@ -148,10 +152,10 @@ LLM_EXPORT int llm_latent_absorb(int dtype, const float *q, long long ldq, const
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_heads <= 65535 && d > 0 && kv_rank > 0 && rot >= 0 && rot % 2 == 0, "latent_absorb: bad sizes");
   LLM_REQUIRE(rot == 0 || (table && table_rows > 0), "latent_absorb: a rotation needs its table");
-  constexpr int THREADS = 256;
+  constexpr int THREADS = 128;
   const size_t smem = (size_t)LAT_TT * d * sizeof(float);
   LLM_REQUIRE(smem <= 96 * 1024, "latent_absorb: heads of %d channels are not supported", d);
-  const dim3 grid((n_tokens + LAT_TT - 1) / LAT_TT, n_heads);
+  const dim3 grid((n_tokens + LAT_TT - 1) / LAT_TT, n_heads, (kv_rank + THREADS - 1) / THREADS);
   if (dtype == LLM_F32) {
     LLM_CHECK_CUDA(llm_allow_smem(latent_absorb_kernel<float, THREADS>, smem), "latent_absorb attribute");
     llm_launch(latent_absorb_kernel<float, THREADS>, grid, dim3(THREADS), smem, stream, q, ldq, (const float *)w_uk, (float *)out, ldo,
@@ -168,7 +172,8 @@ LLM_EXPORT int llm_latent_absorb(int dtype, const float *q, long long ldq, const
 // ---------------------------------------------------------------- the heads' results are expanded by W_uv
 // x [tokens, heads, kv_rank] (the weighted sums of cached latents), w_uv [heads * dv, kv_rank]:
 // out[t, h, j] = sum_c x[t, h, c] * w_uv[h * dv + j, c].  A CTA takes one head and TT tokens; a warp owns output
-// channels, its lanes walk a row of w_uv together (in lane order, then the shuffle tree).
+// channels, its lanes walk a row of w_uv together (in lane order, then the shuffle tree); blockIdx.z shares the
+// output channels out, eight to a CTA.
 constexpr int LAT_ET = 8;
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS)
@@ -185,7 +190,7 @@ latent_expand_kernel(const T *__restrict__ x, long long ldx, const T *__restrict
   }
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int j = warp; j < dv; j += THREADS / 32) {
+  for (int j = blockIdx.z * (THREADS / 32) + warp; j < dv; j += THREADS / 32 * gridDim.z) {
     const T *w = w_uv + ((size_t)h * dv + j) * kv_rank;
     float acc[LAT_ET];
 #pragma unroll
@@ -210,7 +215,7 @@ LLM_EXPORT int llm_latent_expand(int dtype, const void *x, long long ldx, const 
   constexpr int THREADS = 256;
   const size_t smem = (size_t)LAT_ET * kv_rank * sizeof(float);
   LLM_REQUIRE(smem <= 96 * 1024, "latent_expand: a latent of %d channels is not supported", kv_rank);
-  const dim3 grid((n_tokens + LAT_ET - 1) / LAT_ET, n_heads);
+  const dim3 grid((n_tokens + LAT_ET - 1) / LAT_ET, n_heads, std::min(64, (dv + THREADS / 32 - 1) / (THREADS / 32)));
   if (dtype == LLM_F32) {
     LLM_CHECK_CUDA(llm_allow_smem(latent_expand_kernel<float, THREADS>, smem), "latent_expand attribute");
     llm_launch(latent_expand_kernel<float, THREADS>, grid, dim3(THREADS), smem, stream, (const float *)x, ldx, (const float *)w_uv,

@@ -729,59 +729,89 @@ LLM_EXPORT int llm_head_norm_gate(const float *x, long long ldx, const float *we
 //   prep [tokens, heads, 3, d] = w, b, u;  r and beta k into their room of the row;
 //   gate [tokens, heads * dv] = g2 x2, x2 = proj[off_g1 ...] (rank_g values), g2 [heads * dv, rank_g]  (logits; the sigmoid is the
 //   norm kernel's).
-// One CTA a token; sums in lane order then the shuffle tree, whatever the batch.
+// A CTA takes CD_TT tokens and CD_THREADS channels (blockIdx.y counts the runs of channels): a row of a2 or g2 is read
+// once for the CTA's tokens.  Every sum runs in the same order (lanes, then the shuffle tree; the ranks ascending)
+// whatever the batch and the grouping.
 constexpr int CD_THREADS = 256;
+constexpr int CD_TT = 4;
 __device__ __forceinline__ float softplus32(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 __global__ void __launch_bounds__(CD_THREADS)
 channel_delta_prepare_kernel(float *__restrict__ cv, long long ldc, const float *__restrict__ proj, long long ld, int off_b, int off_a1,
                              int rank_a, int off_g1, int rank_g, const float *__restrict__ a2, const float *__restrict__ dt_bias,
                              const float *__restrict__ a_log, const float *__restrict__ g2, float key_eps, float *__restrict__ prep,
-                             float *__restrict__ gate, int n_heads, int n_kv, int d, int dv) {
-  extern __shared__ float cd_sm[];                     // x1 [rank_a] | x2 [rank_g] | inv_q [n_kv] | inv_k [n_kv]
-  float *x1 = cd_sm, *x2 = x1 + rank_a, *inv_q = x2 + rank_g, *inv_k = inv_q + n_kv;
+                             float *__restrict__ gate, int n_tokens, int n_heads, int n_kv, int d, int dv) {
+  extern __shared__ float cd_sm[];                     // x1 [TT][rank_a] | x2 [TT][rank_g] | inv_q [TT][n_kv] | inv_k [TT][n_kv]
+  float *x1 = cd_sm, *x2 = x1 + CD_TT * rank_a, *inv_q = x2 + CD_TT * rank_g, *inv_k = inv_q + CD_TT * n_kv;
   grid_dependents_launch();
   grid_dependency_wait();
-  const int t = blockIdx.x;
-  float *row = cv + (size_t)t * ldc;
-  const float *pr = proj + (size_t)t * ld;
-  for (int i = threadIdx.x; i < rank_a; i += CD_THREADS) x1[i] = pr[off_a1 + i];
-  for (int i = threadIdx.x; i < rank_g; i += CD_THREADS) x2[i] = pr[off_g1 + i];
+  const int t0 = blockIdx.x * CD_TT, nt = min(CD_TT, n_tokens - t0);
+  for (int i = threadIdx.x; i < CD_TT * rank_a; i += CD_THREADS) {
+    const int tt = i / rank_a;
+    x1[i] = tt < nt ? proj[(size_t)(t0 + tt) * ld + off_a1 + (i - tt * rank_a)] : 0.f;
+  }
+  for (int i = threadIdx.x; i < CD_TT * rank_g; i += CD_THREADS) {
+    const int tt = i / rank_g;
+    x2[i] = tt < nt ? proj[(size_t)(t0 + tt) * ld + off_g1 + (i - tt * rank_g)] : 0.f;
+  }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int item = warp; item < 2 * n_kv; item += CD_THREADS / 32) {       // q heads, then k heads
-    const float *x = row + (size_t)item * d;
+  for (int item = warp; item < nt * 2 * n_kv; item += CD_THREADS / 32) {   // per token: q heads, then k heads
+    const int tt = item / (2 * n_kv), which = item - tt * 2 * n_kv;
+    const float *x = cv + (size_t)(t0 + tt) * ldc + (size_t)which * d;
     float ss = 0.f;
     for (int c = lane; c < d; c += 32) ss = fmaf(x[c], x[c], ss);
     ss = warp_sum(ss);
     if (lane == 0) {
-      if (item < n_kv) inv_q[item] = rsqrtf(ss + key_eps) * rsqrtf((float)d);
-      else inv_k[item - n_kv] = rsqrtf(ss + key_eps);
+      if (which < n_kv) inv_q[tt * n_kv + which] = rsqrtf(ss + key_eps) * rsqrtf((float)d);
+      else inv_k[tt * n_kv + which - n_kv] = rsqrtf(ss + key_eps);
     }
   }
   __syncthreads();
   const int group = n_heads / n_kv;
   const int off_v = 2 * n_kv * d, off_r = off_v + n_heads * dv, off_k = off_r + n_heads * d;
-  for (int i = threadIdx.x; i < n_heads * d; i += CD_THREADS) {
+  const int i = blockIdx.y * CD_THREADS + threadIdx.x;
+  if (i < n_heads * d) {
     const int h = i / d, c = i - h * d, g = h / group;
-    const float q = row[g * d + c] * inv_q[g];
-    const float k = row[(n_kv + g) * d + c] * inv_k[g];
-    const float beta = 1.f / (1.f + expf(-pr[off_b + h]));
     const float *a = a2 + (size_t)i * rank_a;
-    float s = 0.f;
-    for (int j = 0; j < rank_a; ++j) s = fmaf(a[j], x1[j], s);
-    const float w = expf(-expf(a_log[h]) * softplus32(s + dt_bias[i]));
-    float *p = prep + ((size_t)t * n_heads + h) * 3 * d;
-    p[c] = w;
-    p[d + c] = beta * k;
-    p[2 * d + c] = w * k;
-    row[off_r + i] = q;
-    row[off_k + i] = beta * k;
+    float s[CD_TT];
+#pragma unroll
+    for (int tt = 0; tt < CD_TT; ++tt) s[tt] = 0.f;
+    for (int j = 0; j < rank_a; ++j) {
+      const float av = a[j];
+#pragma unroll
+      for (int tt = 0; tt < CD_TT; ++tt) s[tt] = fmaf(av, x1[tt * rank_a + j], s[tt]);
+    }
+    const float rate = -expf(a_log[h]), bias = dt_bias[i];
+#pragma unroll
+    for (int tt = 0; tt < CD_TT; ++tt) {
+      if (tt < nt) {
+        float *row = cv + (size_t)(t0 + tt) * ldc;
+        const float q = row[g * d + c] * inv_q[tt * n_kv + g];
+        const float k = row[(n_kv + g) * d + c] * inv_k[tt * n_kv + g];
+        const float beta = 1.f / (1.f + expf(-proj[(size_t)(t0 + tt) * ld + off_b + h]));
+        const float w = expf(rate * softplus32(s[tt] + bias));
+        float *p = prep + ((size_t)(t0 + tt) * n_heads + h) * 3 * d;
+        p[c] = w;
+        p[d + c] = beta * k;
+        p[2 * d + c] = w * k;
+        row[off_r + i] = q;
+        row[off_k + i] = beta * k;
+      }
+    }
   }
-  for (int i = threadIdx.x; i < n_heads * dv; i += CD_THREADS) {
+  if (i < n_heads * dv) {
     const float *a = g2 + (size_t)i * rank_g;
-    float s = 0.f;
-    for (int j = 0; j < rank_g; ++j) s = fmaf(a[j], x2[j], s);
-    gate[(size_t)t * n_heads * dv + i] = s;
+    float s[CD_TT];
+#pragma unroll
+    for (int tt = 0; tt < CD_TT; ++tt) s[tt] = 0.f;
+    for (int j = 0; j < rank_g; ++j) {
+      const float av = a[j];
+#pragma unroll
+      for (int tt = 0; tt < CD_TT; ++tt) s[tt] = fmaf(av, x2[tt * rank_g + j], s[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < CD_TT; ++tt)
+      if (tt < nt) gate[(size_t)(t0 + tt) * n_heads * dv + i] = s[tt];
   }
 }
 
@@ -793,11 +823,13 @@ LLM_EXPORT int llm_channel_delta_prepare(float *cv, long long ldc, const float *
   LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0 && d > 0 && dv > 0 && rank_a > 0 && rank_g > 0,
               "channel_delta_prepare: bad sizes");
   LLM_REQUIRE(ldc >= 2LL * n_kv * d + (long long)n_heads * dv + 2LL * n_heads * d, "channel_delta_prepare: rows too short");
-  const size_t smem = (size_t)(rank_a + rank_g + 2 * n_kv) * sizeof(float);
+  const size_t smem = (size_t)CD_TT * (rank_a + rank_g + 2 * n_kv) * sizeof(float);
   LLM_REQUIRE(smem <= 96 * 1024, "channel_delta_prepare: low-rank inputs of %d and %d values are not supported", rank_a, rank_g);
   LLM_CHECK_CUDA(llm_allow_smem(channel_delta_prepare_kernel, smem), "channel_delta_prepare attribute");
-  llm_launch(channel_delta_prepare_kernel, dim3(n_tokens), dim3(CD_THREADS), smem, stream, cv, ldc, proj, ld, off_b, off_a1, rank_a, off_g1,
-             rank_g, a2, dt_bias, a_log, g2, key_eps, prep, gate, n_heads, n_kv, d, dv);
+  const int widest = n_heads * (d > dv ? d : dv);
+  llm_launch(channel_delta_prepare_kernel, dim3((n_tokens + CD_TT - 1) / CD_TT, (widest + CD_THREADS - 1) / CD_THREADS), dim3(CD_THREADS), smem,
+             stream, cv, ldc, proj, ld, off_b, off_a1, rank_a, off_g1, rank_g, a2, dt_bias, a_log, g2, key_eps, prep, gate, n_tokens, n_heads,
+             n_kv, d, dv);
   LLM_CHECK_LAUNCH("channel_delta_prepare");
   return LLM_OK;
 }

@@ -172,12 +172,13 @@ class LatentAttention : public Mixer {
     kernels::latent_absorb(q, w_uk_.buf.get(), qa, n_heads_, d_, rot_, kv_rank_, table, table_rows, interleaved, ctx.tok_pos, ctx.stream);
     Act mixed = ctx.arena->act(ctx.dtype, T, (int64_t)n_heads_ * kv_rank_);
     if (tc && kernels::latent_decode_supported(kv_rank_, rot_)) {
-      // all heads of a token over the cached rows; long sequences in runs of at least two tiles of keys, enough
-      // of them to fill the device twice; the same for every step of a captured graph
+      // all heads of a token over the cached rows.  A run's partial result is heads x kv_rank 32-bit sums, as many
+      // bytes as some tens of cached rows, so a run takes at least 256 keys; within that, enough runs to give
+      // every multiprocessor a CTA.  The same for every step of a captured graph.
       const int max_len = std::max(ctx.max_kv_len, 1);
       const int ctas = std::max(1, T * ((n_heads_ + 31) / 32));
-      const int want = std::max(1, (2 * ctx.sm_count + ctas - 1) / ctas);
-      const int most = std::max(1, max_len / 128);
+      const int want = std::max(1, (ctx.sm_count + ctas - 1) / ctas);
+      const int most = std::max(1, max_len / 256);
       const int n_splits = std::max(1, std::min(std::min(want, most), 64));
       float *ws = nullptr;
       if (n_splits > 1) ws = ctx.arena->alloc_n<float>(kernels::latent_decode_floats(T, n_heads_, kv_rank_, n_splits));
