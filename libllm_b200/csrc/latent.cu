@@ -121,7 +121,7 @@ latent_absorb_kernel(const float *__restrict__ q, long long ldq, const T *__rest
     float acc[LAT_TT];
 #pragma unroll
     for (int t = 0; t < LAT_TT; ++t) acc[t] = 0.f;
-#pragma unroll 4
+#pragma unroll 16
     for (int i = 0; i < d; ++i) {
       const float wv = to_float(w[(size_t)i * kv_rank + c]);
 #pragma unroll

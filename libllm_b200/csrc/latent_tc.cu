@@ -94,11 +94,12 @@ LLM_EXPORT int llm_latent_rotate_q(const float *q, long long ldq, void *out, lon
 }
 
 // ---------------------------------------------------------------- prompt steps from the first token: materialised heads
-// One CTA takes 64 query rows of one head of one sequence, its four warps 16 rows each; key tiles of 64 rows are
-// walked with two tiles in flight.  q [T, heads * (d + rot)] (rotated), kv [T, heads * d | heads * dv], kr [T, rot]
+// One CTA takes 128 query rows of one head of one sequence, its eight warps 16 rows each; key tiles of 64 rows are
+// walked with two tiles in flight, up to the one that holds the CTA's last row; a warp sits out the tiles that lie
+// wholly behind its rows.  q [T, heads * (d + rot)] (rotated), kv [T, heads * d | heads * dv], kr [T, rot]
 // (rotated), out [T, heads * dv]; sequence b owns rows seq_start[b] .. seq_start[b+1]-1 at positions 0 .. .
 // Key rows are d + rot channels rounded up to 16 (the rest zeros), value rows DVP >= dv channels (the rest zeros).
-constexpr int LP_WARPS = 4;
+constexpr int LP_WARPS = 8;
 constexpr int LP_BM = 16 * LP_WARPS;
 
 template <int DVP>
@@ -130,7 +131,7 @@ latent_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long ldq, const 
   const int rows = min(LP_BM, n_q - r0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int n_iter = tile + 1;                               // key tiles 0 .. the diagonal one
+  const int n_iter = min((n_q + LT_BN - 1) / LT_BN, (r0 + LP_BM) / LT_BN);   // key tiles 0 .. the one with the CTA's last row
   const int d8 = d / 8, dk8 = dk / 8, dv8 = dv / 8;
   const size_t v_off = (size_t)n_heads * d + (size_t)h * dv;
 
@@ -176,6 +177,8 @@ latent_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long ldq, const 
     cp_async_wait<1>();
     __syncthreads();
     const __nv_bfloat16 *tk = sK + stage * LT_BN * ldk, *tv = sV + stage * LT_BN * LDV;
+    const int k0 = it * LT_BN;
+    if (k0 <= r0 + warp * 16 + 15) {                         // else: no row of this warp sees a key of the tile
 
     float s[NT][4];
 #pragma unroll
@@ -195,8 +198,7 @@ latent_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long ldq, const 
       }
     }
 
-    if (it == n_iter - 1) {                                  // the diagonal tile: key j is seen by the row at p when j <= p
-      const int k0 = it * LT_BN;
+    if (k0 + LT_BN - 1 > r0 + warp * 16) {                   // a tile on the diagonal: key j is seen by the row at p when j <= p
 #pragma unroll
       for (int n = 0; n < NT; ++n)
 #pragma unroll
@@ -255,6 +257,7 @@ latent_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long ldq, const 
         mma16816(o[2 * d2], pa, vb[0], vb[1]);
         mma16816(o[2 * d2 + 1], pa, vb[2], vb[3]);
       }
+    }
     }
     __syncthreads();
   }
@@ -538,25 +541,41 @@ latent_decode_kernel(const __nv_bfloat16 *__restrict__ qa, long long ldq, const 
   }
 }
 
-// out[t, h, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = 2^(m_s - max m): one CTA per (token, head).
+// out[t, h, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = 2^(m_s - max m): one CTA per (token, head).  The runs'
+// weights go through shared memory once, so that the loads of the partial sums are independent of one another.
+constexpr int LJ_MAX = 64;               // runs at most
 __global__ void __launch_bounds__(128)
 latent_join_kernel(const float *__restrict__ ws_o, const float *__restrict__ ws_ml, int n_splits, int kv_rank,
                    __nv_bfloat16 *__restrict__ out, long long ldo, int n_heads) {
+  __shared__ float w[LJ_MAX];
+  __shared__ float inv_s;
   grid_dependents_launch();
   grid_dependency_wait();
   const int h = blockIdx.x, tok = blockIdx.y;
   const float *ml = ws_ml + ((size_t)tok * n_heads + h) * n_splits * 2;
   const float *po = ws_o + ((size_t)tok * n_heads + h) * n_splits * (size_t)kv_rank;
-  float m = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml[2 * s]);
-  float l = 0.f;
-  for (int s = 0; s < n_splits; ++s)
-    if (ml[2 * s] != -INFINITY) l += exp2f(ml[2 * s] - m) * ml[2 * s + 1];
-  const float inv = 1.f / l;
+  if (threadIdx.x < 32) {
+    float m = -INFINITY;
+    for (int s = threadIdx.x; s < n_splits; s += 32) m = fmaxf(m, ml[2 * s]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    for (int s = threadIdx.x; s < n_splits; s += 32) w[s] = ml[2 * s] == -INFINITY ? 0.f : exp2f(ml[2 * s] - m);
+    __syncwarp();
+    if (threadIdx.x == 0) {
+      float l = 0.f;
+      for (int s = 0; s < n_splits; ++s) l = fmaf(w[s], ml[2 * s + 1], l);       // in the order of the runs
+      inv_s = 1.f / l;
+    }
+  }
+  __syncthreads();
+  const float inv = inv_s;
   for (int c = threadIdx.x; c < kv_rank; c += 128) {
     float acc = 0.f;
-    for (int s = 0; s < n_splits; ++s)
-      if (ml[2 * s] != -INFINITY) acc = fmaf(exp2f(ml[2 * s] - m), po[(size_t)s * kv_rank + c], acc);
+#pragma unroll 8
+    for (int s = 0; s < n_splits; ++s) {
+      const float v = po[(size_t)s * kv_rank + c];
+      acc = w[s] != 0.f ? fmaf(w[s], v, acc) : acc;        // a run without keys left nothing there
+    }
     out[(size_t)tok * ldo + (size_t)h * kv_rank + c] = __float2bfloat16(acc * inv);
   }
 }
@@ -597,7 +616,7 @@ LLM_EXPORT int llm_latent_decode(const void *qa, long long ldq, const void *cach
                                  float scale, void *out, long long ldo, float *ws, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(llm_latent_decode_supports(kv_rank, rot), "latent_decode: rows of %d + %d channels are not supported", kv_rank, rot);
-  LLM_REQUIRE(n_tokens > 0 && n_tokens <= 65535 && n_heads > 0 && page_size > 0 && n_splits >= 1 && ldq % 8 == 0 && ldo % 2 == 0 &&
+  LLM_REQUIRE(n_tokens > 0 && n_tokens <= 65535 && n_heads > 0 && page_size > 0 && n_splits >= 1 && n_splits <= LJ_MAX && ldq % 8 == 0 && ldo % 2 == 0 &&
                   (n_splits == 1 || ws),
               "latent_decode: bad sizes");
   const int row = kv_rank + rot;
