@@ -191,6 +191,8 @@ void register_builtin_architectures() {
   register_sesuzen_architecture();
   extern void register_sobezen_architecture();     // config/sobezen.cc
   register_sobezen_architecture();
+  extern void register_tazizen_architecture();     // config/tazizen.cc
+  register_tazizen_architecture();
 }
 
 }  // namespace llm

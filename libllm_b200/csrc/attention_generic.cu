@@ -67,7 +67,7 @@ attention_generic_kernel(const T *__restrict__ q, long long q_stride, T *__restr
                          const int *__restrict__ tok_pos, const int *__restrict__ page_table,
                          int pt_stride, int n_tokens, int n_heads, int n_kv, int d, int dv, int page_size,
                          int window, int block, int sink, float scale, const float *__restrict__ gate,
-                         long long gate_stride, int vec, int v_ld) {
+                         long long gate_stride, int vec, int v_ld, float null_score) {
   __shared__ __align__(16) float q_s[WARPS][MAX_D];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long w = (long long)blockIdx.x * WARPS + warp;
@@ -122,6 +122,12 @@ attention_generic_kernel(const T *__restrict__ q, long long q_stride, T *__restr
     }
   }
   T *orow = out + (size_t)token * out_stride + (size_t)h * dv;
+  if (null_score > -INFINITY) {     // one more key whose score is null_score and whose value is nought
+    const float m_new = fmaxf(m, null_score), alpha = expf(m - m_new);
+    l = l * alpha + expf(null_score - m_new);
+#pragma unroll
+    for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= alpha;
+  }
   float inv = 1.f / l;
   if (gate) inv *= 1.f / (1.f + expf(-gate[(size_t)token * gate_stride + h]));
 #pragma unroll
@@ -138,7 +144,7 @@ LLM_EXPORT int llm_attention_generic_ld(int dtype, const void *q, long long q_st
                                         const int *tok_seq, const int *tok_pos, const int *page_table,
                                         int pt_stride, int n_tokens, int n_heads, int n_kv, int d, int dv, int v_ld,
                                         int page_size, int window, int block, int sink, float scale, const float *gate,
-                                        long long gate_stride, cudaStream_t stream) {
+                                        long long gate_stride, float null_score, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0, "attention: bad head counts %d/%d", n_heads, n_kv);
   LLM_REQUIRE(d > 0 && d <= MAX_D_LARGE && dv > 0 && dv <= MAX_D_LARGE, "attention: head sizes %d / %d are not supported (up to %d)", d, dv,
@@ -155,7 +161,7 @@ LLM_EXPORT int llm_attention_generic_ld(int dtype, const void *q, long long q_st
 #define GENERIC_GO(T, MAXD)                                                                                              \
   attention_generic_kernel<T, MAXD><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(                                          \
       (const T *)q, q_stride, (T *)out, out_stride, (const T *)kcache, (const T *)vcache, tok_seq, tok_pos, page_table, pt_stride, \
-      n_tokens, n_heads, n_kv, d, dv, page_size, window, block, sink, scale, gate, gate_stride, vec, v_ld)
+      n_tokens, n_heads, n_kv, d, dv, page_size, window, block, sink, scale, gate, gate_stride, vec, v_ld, null_score)
   if (dtype == LLM_F32 && small) GENERIC_GO(float, MAX_D_SMALL);
   else if (dtype == LLM_F32) GENERIC_GO(float, MAX_D_LARGE);
   else if (dtype == LLM_BF16 && small) GENERIC_GO(__nv_bfloat16, MAX_D_SMALL);
@@ -173,5 +179,5 @@ LLM_EXPORT int llm_attention_generic(int dtype, const void *q, long long q_strid
                                      int page_size, int window, int block, int sink, float scale, const float *gate,
                                      long long gate_stride, cudaStream_t stream) {
   return llm_attention_generic_ld(dtype, q, q_stride, out, out_stride, kcache, vcache, tok_seq, tok_pos, page_table, pt_stride,
-                                  n_tokens, n_heads, n_kv, d, dv, dv, page_size, window, block, sink, scale, gate, gate_stride, stream);
+                                  n_tokens, n_heads, n_kv, d, dv, dv, page_size, window, block, sink, scale, gate, gate_stride, -INFINITY, stream);
 }

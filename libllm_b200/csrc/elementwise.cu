@@ -1054,3 +1054,168 @@ LLM_EXPORT int llm_head_gate(void *x, int dtype, long long ld, const float *gate
   LLM_CHECK_LAUNCH("head_gate");
   return LLM_OK;
 }
+
+// ---------------------------------------------------------------- several residual streams
+// A model that carries S copies x_0 .. x_{S-1} of the residual stream ("hyper-connections") joins a
+// sublayer to them with three small tensors: what the sublayer reads is u = sum_s a[s] x_s, and its
+// result y moves every stream at once, from the old ones: x_t <- sum_s M[s, t] x_s + o[t] y.  One CTA
+// per row does, in this order and all in 32-bit:
+//   1. the pending move of the sublayer before (delta != null: y = (sum of delta's parts + col_bias) *
+//      col_scale with matrix `mix` [S, S] indexed [from, to] and vector `outw` [S]); the new streams are
+//      stored (x_out; in place when x_out is x_in and rows is null)
+//   2. u = sum_s inw[s] x_s, or the plain sum of the streams when inw is null
+//   3. out = u / sqrt(mean(u^2) + eps) * norm_w in out's type, or u itself (32-bit) when norm_w is null.
+// in_stride 0: the S streams are all equal to the one at x_in (a model's first layer).  With `rows`, output
+// row i is source row rows[i] and x_out holds the n_rows chosen rows only (out_stride apart per stream).
+// A row's result depends on that row alone; every sum has a fixed order.
+constexpr int HYPER_MAX_STREAMS = 8;
+template <typename TO, int THREADS, int VEC>
+__global__ void __launch_bounds__(THREADS)
+hyper_mix_norm_kernel(const float *__restrict__ x_in, long long in_stride, float *__restrict__ x_out, long long out_stride, int S,
+                      const float *__restrict__ delta, int n_parts, size_t part_stride, const float *__restrict__ col_scale,
+                      const float *__restrict__ col_bias, const float *__restrict__ mix, const float *__restrict__ outw,
+                      const float *__restrict__ inw, const float *__restrict__ norm_w, float eps, TO *__restrict__ out,
+                      const int *__restrict__ rows, int hidden) {
+  extern __shared__ float row_buf[];   // hidden floats
+  __shared__ float scratch[THREADS / 32 + 1];
+  __shared__ float s_mix[HYPER_MAX_STREAMS * HYPER_MAX_STREAMS], s_out[HYPER_MAX_STREAMS], s_in[HYPER_MAX_STREAMS];
+  grid_dependents_launch();
+  if (threadIdx.x < S * S) s_mix[threadIdx.x] = delta ? mix[threadIdx.x] : 0.f;       // weights: written when the model was loaded
+  if (threadIdx.x < S) {
+    s_out[threadIdx.x] = delta ? outw[threadIdx.x] : 0.f;
+    s_in[threadIdx.x] = inw ? inw[threadIdx.x] : 1.f;
+  }
+  grid_dependency_wait();
+  __syncthreads();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  const bool store = x_out != nullptr && (delta != nullptr || x_out != x_in || rows != nullptr || in_stride == 0);
+  float ss = 0.f;
+  for (int c = threadIdx.x * VEC; c < hidden; c += THREADS * VEC) {
+    float xs[HYPER_MAX_STREAMS][VEC];
+#pragma unroll
+    for (int s = 0; s < HYPER_MAX_STREAMS; ++s)
+      if (s < S) {
+        const float *p = x_in + (size_t)s * in_stride + (size_t)r * hidden + c;
+        if (VEC == 4) {
+          const float4 v = *reinterpret_cast<const float4 *>(p);
+          xs[s][0] = v.x, xs[s][1 % VEC] = v.y, xs[s][2 % VEC] = v.z, xs[s][3 % VEC] = v.w;
+        } else {
+          xs[s][0] = *p;
+        }
+      }
+    float y[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) y[k] = 0.f;
+    if (delta) {
+      for (int p = 0; p < n_parts; ++p) {
+        const float *dp = delta + p * part_stride + (size_t)r * hidden + c;
+        if (VEC == 4) {
+          const float4 v = *reinterpret_cast<const float4 *>(dp);
+          y[0] += v.x, y[1 % VEC] += v.y, y[2 % VEC] += v.z, y[3 % VEC] += v.w;
+        } else {
+          y[0] += *dp;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        if (col_bias) y[k] += col_bias[c + k];
+        if (col_scale) y[k] *= col_scale[c + k];
+      }
+    }
+    float u[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) u[k] = 0.f;
+#pragma unroll
+    for (int t = 0; t < HYPER_MAX_STREAMS; ++t)
+      if (t < S) {
+        float nv[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          if (delta) {
+            float a = 0.f;
+#pragma unroll
+            for (int s = 0; s < HYPER_MAX_STREAMS; ++s)
+              if (s < S) a = fmaf(s_mix[s * S + t], xs[s][k], a);
+            nv[k] = fmaf(s_out[t], y[k], a);
+          } else {
+            nv[k] = xs[t][k];
+          }
+          u[k] = fmaf(s_in[t], nv[k], u[k]);
+        }
+        if (store) {
+          float *q = x_out + (size_t)t * out_stride + (size_t)i * hidden + c;
+          if (VEC == 4) *reinterpret_cast<float4 *>(q) = make_float4(nv[0], nv[1 % VEC], nv[2 % VEC], nv[3 % VEC]);
+          else *q = nv[0];
+        }
+      }
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      row_buf[c + k] = u[k];
+      ss = fmaf(u[k], u[k], ss);
+    }
+  }
+  if (!out) return;
+  if (!norm_w) {
+    __syncthreads();
+    for (int c = threadIdx.x; c < hidden; c += THREADS) out[(size_t)i * hidden + c] = from_float<TO>(row_buf[c]);
+    return;
+  }
+  const float total = block_sum<THREADS>(ss, scratch);
+  const float inv = rsqrtf(total / (float)hidden + eps);
+  TO *o = out + (size_t)i * hidden;
+  for (int c = threadIdx.x; c < hidden; c += THREADS) o[c] = from_float<TO>(row_buf[c] * inv * norm_w[c]);
+}
+
+template <typename TO>
+static int launch_hyper(const float *x_in, long long in_stride, float *x_out, long long out_stride, int S, const float *delta,
+                        int n_parts, size_t part_stride, const float *col_scale, const float *col_bias, const float *mix,
+                        const float *outw, const float *inw, const float *norm_w, float eps, TO *out, const int *rows, int n_rows,
+                        int hidden, cudaStream_t stream) {
+  const size_t smem = (size_t)hidden * sizeof(float);
+  LLM_REQUIRE(smem <= 200 * 1024, "hyper_mix_norm: a row of %d values does not fit shared memory", hidden);
+  const bool vec = hidden % 4 == 0 && in_stride % 4 == 0 && out_stride % 4 == 0 && part_stride % 4 == 0 && (uintptr_t)x_in % 16 == 0 &&
+                   (uintptr_t)x_out % 16 == 0 && (uintptr_t)delta % 16 == 0;
+  if (vec) {
+    auto kern = hyper_mix_norm_kernel<TO, 256, 4>;
+    LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "hyper_mix_norm attribute");
+    llm_launch(kern, dim3(n_rows), dim3(256), smem, stream, x_in, in_stride, x_out, out_stride, S, delta, n_parts, part_stride, col_scale,
+               col_bias, mix, outw, inw, norm_w, eps, out, rows, hidden);
+  } else {
+    auto kern = hyper_mix_norm_kernel<TO, 256, 1>;
+    LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "hyper_mix_norm attribute");
+    llm_launch(kern, dim3(n_rows), dim3(256), smem, stream, x_in, in_stride, x_out, out_stride, S, delta, n_parts, part_stride, col_scale,
+               col_bias, mix, outw, inw, norm_w, eps, out, rows, hidden);
+  }
+  LLM_CHECK_LAUNCH("hyper_mix_norm");
+  return LLM_OK;
+}
+
+LLM_EXPORT int llm_hyper_mix_norm(const float *x_in, long long in_stride, float *x_out, long long out_stride, int n_streams,
+                                  const float *delta, int n_parts, long long part_stride, const float *col_scale,
+                                  const float *col_bias, const float *mix, const float *outw, const float *inw, const float *norm_w,
+                                  float eps, void *out, int out_dtype, const int *rows, int n_rows, int hidden, cudaStream_t stream) {
+  if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && hidden > 0 && n_streams >= 1 && n_streams <= HYPER_MAX_STREAMS, "hyper_mix_norm: %d streams of %d x %d (up to %d streams)",
+              n_streams, n_rows, hidden, HYPER_MAX_STREAMS);
+  LLM_REQUIRE(x_in != nullptr && (delta == nullptr || (mix != nullptr && outw != nullptr && n_parts > 0)), "hyper_mix_norm: a pending result needs its matrix and vector");
+  LLM_REQUIRE(norm_w == nullptr || out != nullptr, "hyper_mix_norm: a norm needs a place for its result");
+  if (out_dtype == LLM_BF16 && norm_w)
+    return launch_hyper<__nv_bfloat16>(x_in, in_stride, x_out, out_stride, n_streams, delta, n_parts, (size_t)part_stride, col_scale, col_bias,
+                                       mix, outw, inw, norm_w, eps, (__nv_bfloat16 *)out, rows, n_rows, hidden, stream);
+  LLM_REQUIRE(out_dtype == LLM_F32 || out == nullptr, "hyper_mix_norm: the streams' sum is 32-bit");
+  return launch_hyper<float>(x_in, in_stride, x_out, out_stride, n_streams, delta, n_parts, (size_t)part_stride, col_scale, col_bias, mix, outw,
+                             inw, norm_w, eps, (float *)out, rows, n_rows, hidden, stream);
+}
+
+// x[i] += value: a stored norm weight w that is applied as (offset + w).
+__global__ void add_scalar_kernel(float *__restrict__ x, long long n, float value) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] += value;
+}
+LLM_EXPORT int llm_add_scalar(float *x, long long n, float value, cudaStream_t stream) {
+  if (n <= 0) return LLM_OK;
+  const long long blocks = (n + 255) / 256;
+  add_scalar_kernel<<<(unsigned)(blocks > 1024 ? 1024 : blocks), 256, 0, stream>>>(x, n, value);
+  LLM_CHECK_LAUNCH("add_scalar");
+  return LLM_OK;
+}

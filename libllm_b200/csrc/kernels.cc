@@ -172,6 +172,20 @@ void copy_words(const int *src, int *dst, int n, cudaStream_t s) { LLM_CALL("ele
 void gather_words(const int *src1, int n1, const int *src2, int n2, int *dst, cudaStream_t s) {
   LLM_CALL("elementwise", llm_gather_words, src1, n1, src2, n2, dst, s);
 }
+LLM_KERNEL("elementwise", llm_hyper_mix_norm, const float *, long long, float *, long long, int, const float *, int, long long,
+           const float *, const float *, const float *, const float *, const float *, const float *, float, void *, int, const int *, int,
+           int, cudaStream_t)
+LLM_KERNEL("elementwise", llm_add_scalar, float *, long long, float, cudaStream_t)
+void hyper_mix_norm(const float *x_in, long long in_stride, float *x_out, long long out_stride, int n_streams, const Act *delta,
+                    const float *mix, const float *outw, const float *inw, const float *norm_w, float eps, void *out, DType out_dtype,
+                    const int *rows, int n_rows, int hidden, cudaStream_t s) {
+  const bool has = delta && delta->data;
+  if (has && delta->dtype != DType::F32) LLM_THROW(InvalidArg, "hyper_mix_norm: a pending result is 32-bit");
+  LLM_CALL("elementwise", llm_hyper_mix_norm, x_in, in_stride, x_out, out_stride, n_streams, has ? (const float *)delta->data : nullptr,
+           has ? delta->parts : 0, has ? (long long)delta->part_stride : 0, has ? delta->col_scale : nullptr,
+           has ? delta->col_bias : nullptr, mix, outw, inw, norm_w, eps, out, code(out_dtype), rows, n_rows, hidden, s);
+}
+void add_scalar(float *x, long long n, float value, cudaStream_t s) { LLM_CALL("elementwise", llm_add_scalar, x, n, value, s); }
 void add_rmsnorm(float *resid, const Act *delta, const float *weight, float eps, void *out, DType out_dtype, const int *rows,
                  int n_rows, int hidden, cudaStream_t s) {
   const bool has = delta && delta->data;
@@ -297,6 +311,15 @@ void rope_cache_write(const Act &qkv, const Act &q_out, int n_heads, int n_kv, i
            pt_stride, kcache, vcache, page_size, write_cache ? 1 : 0, s);
 }
 
+LLM_KERNEL("rope", llm_rope_headnorm_place, int, int, const void *, long long, void *, long long, int, int, int, int, int, float,
+           const float *, int, int, const int *, const int *, const int *, int, void *, void *, int, int, cudaStream_t)
+void rope_headnorm_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, int dv, float eps, const float *table,
+                         int table_rows, int rot_dim, const int *tok_seq, const int *tok_pos, const int *page_table, int pt_stride,
+                         void *kcache, void *vcache, int page_size, bool write_cache, cudaStream_t s) {
+  LLM_CALL("rope", llm_rope_headnorm_place, code(qkv.dtype), code(q_out.dtype), qkv.data, (long long)qkv.ld, q_out.data,
+           (long long)q_out.ld, (int)qkv.rows, n_heads, n_kv, d, dv, eps, table, table_rows, rot_dim, tok_seq, tok_pos, page_table,
+           pt_stride, kcache, vcache, page_size, write_cache ? 1 : 0, s);
+}
 LLM_KERNEL("rope", llm_qk_place, int, int, const void *, long long, void *, long long, int, int, int, int, int, const float *,
            const float *, float, const float *, int, int, const int *, const int *, const int *, int, void *, void *, int, int,
            cudaStream_t)
@@ -331,7 +354,7 @@ void rope_pairs_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, i
 // ---------------------------------------------------------------- attention
 LLM_KERNEL("attention_generic", llm_attention_generic_ld, int, const void *, long long, void *, long long, const void *, const void *,
            const int *, const int *, const int *, int, int, int, int, int, int, int, int, int, int, int, float, const float *, long long,
-           cudaStream_t)
+           float, cudaStream_t)
 LLM_KERNEL("attention_decode", llm_attention_decode_sink, const void *, long long, void *, long long, const void *, const void *,
            const int *, const int *, int, int, int, int, int, int, int, int, int, int, int, float, float *, float *, const float *,
            long long, int, cudaStream_t)
@@ -350,10 +373,11 @@ LLM_KERNEL("attention_prefill_tc", llm_attention_prefill_tc, const void *, long 
 
 void attention_generic(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_seq, const int *tok_pos,
                        const int *page_table, int pt_stride, int n_heads, int n_kv, int d, int dv, int page_size, int window,
-                       int block, float scale, const float *gate, long long gate_stride, cudaStream_t s, int sink, int v_ld) {
+                       int block, float scale, const float *gate, long long gate_stride, cudaStream_t s, int sink, int v_ld,
+                       float null_score) {
   LLM_CALL("attention_generic", llm_attention_generic_ld, code(q.dtype), q.data, (long long)q.ld, out.data, (long long)out.ld, kc, vc,
            tok_seq, tok_pos, page_table, pt_stride, (int)q.rows, n_heads, n_kv, d, dv, v_ld > 0 ? v_ld : dv, page_size, window, block,
-           sink, scale, gate, gate_stride, s);
+           sink, scale, gate, gate_stride, null_score, s);
 }
 
 // ---------------------------------------------------------------- latent attention
@@ -386,9 +410,9 @@ LLM_KERNEL("latent_tc", llm_latent_rows, const void *, int, int, int, const int 
 LLM_KERNEL("latent_tc", llm_latent_rotate_q, const float *, long long, void *, long long, int, int, int, int, const float *, int, int,
            const int *, cudaStream_t)
 LLM_KERNEL("latent_tc", llm_latent_prefill, const void *, long long, const void *, long long, const void *, void *, long long, const int *,
-           int, int, int, int, int, int, float, cudaStream_t)
+           int, int, int, int, int, int, float, int, cudaStream_t)
 LLM_KERNEL("latent_tc", llm_latent_decode, const void *, long long, const void *, int, const int *, const int *, const int *, int, int,
-           int, int, int, int, float, void *, long long, float *, cudaStream_t)
+           int, int, int, int, float, void *, long long, float *, int, cudaStream_t)
 void latent_rows(const void *cache, int page_size, int row, int kv_rank, const int *tok_seq, const int *tok_pos, const int *page_table,
                  int pt_stride, int n_tokens, const Act &c_out, const Act &kr_out, cudaStream_t s) {
   if (c_out.dtype != DType::BF16 || c_out.ld != kv_rank || (row > kv_rank && (kr_out.dtype != DType::BF16 || kr_out.ld != row - kv_rank)))
@@ -407,11 +431,11 @@ bool latent_prefill_supported(int d, int rot, int dv) {
   return f(d, rot, dv) != 0;
 }
 void latent_prefill(const Act &q, const Act &kv, const Act &kr, const Act &out, const int *seq_start, int n_seqs, int max_q_len,
-                    int n_heads, int d, int rot, int dv, float scale, cudaStream_t s) {
+                    int n_heads, int d, int rot, int dv, float scale, cudaStream_t s, int window) {
   if (q.dtype != DType::BF16 || kv.dtype != DType::BF16 || out.dtype != DType::BF16 || (rot > 0 && (kr.dtype != DType::BF16 || kr.ld != rot)))
     LLM_THROW(InvalidArg, "latent_prefill: bfloat16 operands");
   LLM_CALL("latent_tc", llm_latent_prefill, q.data, (long long)q.ld, kv.data, (long long)kv.ld, kr.data, out.data, (long long)out.ld,
-           seq_start, n_seqs, max_q_len, n_heads, d, rot, dv, scale, s);
+           seq_start, n_seqs, max_q_len, n_heads, d, rot, dv, scale, window, s);
 }
 bool latent_decode_supported(int kv_rank, int rot) {
   static auto f = resolve<int (*)(int, int)>("latent_tc", "llm_latent_decode_supports");
@@ -421,10 +445,11 @@ size_t latent_decode_floats(int n_tokens, int n_heads, int kv_rank, int n_splits
   return n_splits <= 1 ? 0 : (size_t)n_tokens * n_heads * n_splits * ((size_t)kv_rank + 2);
 }
 void latent_decode(const Act &qa, const void *cache, int page_size, const int *tok_seq, const int *tok_pos, const int *page_table,
-                   int pt_stride, int n_heads, int kv_rank, int rot, int n_splits, float scale, const Act &out, float *ws, cudaStream_t s) {
+                   int pt_stride, int n_heads, int kv_rank, int rot, int n_splits, float scale, const Act &out, float *ws, cudaStream_t s,
+                   int window) {
   if (qa.dtype != DType::BF16 || out.dtype != DType::BF16) LLM_THROW(InvalidArg, "latent_decode: bfloat16 operands");
   LLM_CALL("latent_tc", llm_latent_decode, qa.data, (long long)qa.ld, cache, page_size, tok_seq, tok_pos, page_table, pt_stride,
-           (int)qa.rows, n_heads, kv_rank, rot, n_splits, scale, out.data, (long long)out.ld, ws, s);
+           (int)qa.rows, n_heads, kv_rank, rot, n_splits, scale, out.data, (long long)out.ld, ws, window, s);
 }
 bool attention_decode_supported(int d, int group) {
   static auto f = resolve<int (*)(int, int)>("attention_decode", "llm_attention_decode_supports");
@@ -482,6 +507,17 @@ void attention_prefill_tc(const Act &q, const Act &out, const void *kc, const vo
 // ---------------------------------------------------------------- routed feed-forward
 LLM_KERNEL("moe", llm_activation, int, int, const void *, void *, long long, int, cudaStream_t)
 LLM_KERNEL("moe", llm_moe_route, const float *, long long, int, int, int, int, int, int *, float *, cudaStream_t)
+LLM_KERNEL("moe", llm_moe_route_grouped, const float *, long long, int, int, int, int, const float *, int, int, int, int, float, float,
+           int *, float *, cudaStream_t)
+LLM_KERNEL("moe", llm_row_gate, const float *, float *, const float *, long long, int, int, cudaStream_t)
+void moe_route_grouped(const Act &logits, int n_experts, int top, int score, const float *correction, int n_groups, int keep,
+                       int group_top, bool renormalize, float norm_eps, float route_scale, int *chosen, float *weight, cudaStream_t s) {
+  LLM_CALL("moe", llm_moe_route_grouped, (const float *)logits.data, (long long)logits.ld, (int)logits.rows, n_experts, top, score,
+           correction, n_groups, keep, group_top, renormalize ? 1 : 0, norm_eps, route_scale, chosen, weight, s);
+}
+void row_gate(const float *x, float *out, const float *gate, long long gate_stride, int n_rows, int cols, cudaStream_t s) {
+  LLM_CALL("moe", llm_row_gate, x, out, gate, gate_stride, n_rows, cols, s);
+}
 LLM_KERNEL("moe", llm_moe_sort, const int *, int, int, int, int *, int *, int *, cudaStream_t)
 LLM_KERNEL("moe", llm_moe_rows, int, const void *, long long, const void *, const void *, const int *, const float *, int, int, int,
            int, int, int, int, float *, cudaStream_t)

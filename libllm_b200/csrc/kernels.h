@@ -32,6 +32,13 @@ void copy_words(const int *src, int *dst, int n, cudaStream_t s);
 void gather_words(const int *src1, int n1, const int *src2, int n2, int *dst, cudaStream_t s);
 void add_rmsnorm(float *resid, const Act *delta, const float *weight, float eps, void *out, DType out_dtype,
                  const int *rows, int n_rows, int hidden, cudaStream_t s);
+// Several residual streams [n_streams][rows][hidden] (in_stride / out_stride floats apart; in_stride 0: all equal to x_in):
+// applies the pending result `delta` (x_t <- sum_s mix[s, t] x_s + outw[t] y), then u = sum_s inw[s] x_s (inw null: the plain
+// sum) and out = rmsnorm(u) * norm_w, or u itself in 32-bit when norm_w is null.  With `rows`, x_out and out hold those rows only.
+void hyper_mix_norm(const float *x_in, long long in_stride, float *x_out, long long out_stride, int n_streams, const Act *delta,
+                    const float *mix, const float *outw, const float *inw, const float *norm_w, float eps, void *out, DType out_dtype,
+                    const int *rows, int n_rows, int hidden, cudaStream_t s);
+void add_scalar(float *x, long long n, float value, cudaStream_t s);
 // The same pass with a layer norm: (v - mean) / sqrt(var + eps) * weight + bias (bias may be null).
 void add_layernorm(float *resid, const Act *delta, const float *weight, const float *bias, float eps, void *out, DType out_dtype,
                    const int *rows, int n_rows, int hidden, cudaStream_t s);
@@ -93,6 +100,12 @@ void rope_cache_write(const Act &qkv, const Act &q_out, int n_heads, int n_kv, i
 void qk_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, int dv, const float *q_norm, const float *k_norm,
               float eps, const float *table, int table_rows, int rot_dim, const int *tok_seq, const int *tok_pos,
               const int *page_table, int pt_stride, void *kcache, void *vcache, int page_size, bool write_cache, cudaStream_t s);
+// Rows [q | k | v (n_kv * dv) | ...]: rotation of the first rot_dim channels of each q and k head (pairs i, i + rot_dim/2), THEN
+// every q and k head divided by its root mean square over d (sqrt(mean + eps), no weight; eps < 0: no norm), q -> q_out,
+// k and v appended to the cache.
+void rope_headnorm_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, int dv, float eps, const float *table,
+                         int table_rows, int rot_dim, const int *tok_seq, const int *tok_pos, const int *page_table, int pt_stride,
+                         void *kcache, void *vcache, int page_size, bool write_cache, cudaStream_t s);
 // Rows [q | k | v | ...] without a rotation: adds `bias` (one 32-bit value per stacked row; null: none), divides each
 // value head by its root mean square when v_eps >= 0, writes q and appends k, v to the cache.
 // rows [q | k | v] (no v part with values_from_keys: the value cache gets the key as projected); bias over the row's columns
@@ -104,13 +117,17 @@ void kv_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, in
               const int *tok_seq, const int *tok_pos, const int *page_table, int pt_stride, void *kcache, void *vcache,
               int page_size, bool write_cache, cudaStream_t s);
 // ---- attention
+constexpr float NO_NULL_KEY = -__builtin_huge_valf();
 // Masks: `window` > 0, a query sees the last `window` keys; `block` > 0, only keys of its own block
 // of `block` positions counted from 0; `sink` > 0 (with a window): the first `sink` positions stay visible.  `gate` (32-bit, one value per token and head, row stride
 // gate_stride; null: none): the head's result is multiplied by sigmoid(gate).
 void attention_generic(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_seq, const int *tok_pos,
                        const int *page_table, int pt_stride, int n_heads, int n_kv, int d, int dv, int page_size, int window,
-                       int block, float scale, const float *gate, long long gate_stride, cudaStream_t s, int sink = 0, int v_ld = 0);
+                       int block, float scale, const float *gate, long long gate_stride, cudaStream_t s, int sink = 0, int v_ld = 0,
+                       float null_score = NO_NULL_KEY);
 // v_ld > 0: value rows lie v_ld channels apart (the values are the first dv channels of the key rows when vc is kc).
+// null_score: every query also sees one key of that score that has no value (exp(null_score) joins the softmax's
+// denominator); NO_NULL_KEY: none.
 // ---- latent attention (csrc/latent.cu): attention over one cached row [c | k_r] per position that every head reads
 // proj rows (32-bit) hold the query latent at off_q and, with off_kv >= 0, the key/value latent and the shared key part;
 // cq_out = rms(query latent) * q_weight; the token's cache row = [rms(first kv_rank) * kv_weight | rotated last rot].
@@ -132,12 +149,13 @@ void latent_rotate_q(const Act &q, const Act &out, int n_heads, int d, int rot, 
 bool latent_prefill_supported(int d, int rot, int dv);
 // Sequences that start at their first token, heads materialised: kv [T, heads * d | heads * dv], kr [T, rot] rotated.
 void latent_prefill(const Act &q, const Act &kv, const Act &kr, const Act &out, const int *seq_start, int n_seqs, int max_q_len,
-                    int n_heads, int d, int rot, int dv, float scale, cudaStream_t s);
+                    int n_heads, int d, int rot, int dv, float scale, cudaStream_t s, int window = 0);
 bool latent_decode_supported(int kv_rank, int rot);
 size_t latent_decode_floats(int n_tokens, int n_heads, int kv_rank, int n_splits);
 // qa [T, heads * (kv_rank + rot)] (latent_absorb) over the cached rows -> out [T, heads * kv_rank]; ws: latent_decode_floats
 void latent_decode(const Act &qa, const void *cache, int page_size, const int *tok_seq, const int *tok_pos, const int *page_table,
-                   int pt_stride, int n_heads, int kv_rank, int rot, int n_splits, float scale, const Act &out, float *ws, cudaStream_t s);
+                   int pt_stride, int n_heads, int kv_rank, int rot, int n_splits, float scale, const Act &out, float *ws, cudaStream_t s,
+                   int window = 0);
 bool attention_decode_supported(int d, int group);
 void attention_decode(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                       int pt_stride, int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window,
@@ -165,6 +183,12 @@ enum Activation { GeluErf = 0, GeluTanh = 1, Silu = 2, Relu2 = 3 };
 void activation(const Act &in, const Act &out, int act, cudaStream_t s);
 // logits [T, E] 32-bit -> chosen [T * top], weight [T * top]; score 0 sigmoid, 1 softmax
 void moe_route(const Act &logits, int n_experts, int top, int score, bool renormalize, int *chosen, float *weight, cudaStream_t s);
+// The choice on s + correction (null: none) among the experts of the `keep` best of n_groups groups (a group's score: the sum of
+// its group_top largest corrected scores); weights s, with `renormalize` s / (sum + norm_eps), times route_scale.
+void moe_route_grouped(const Act &logits, int n_experts, int top, int score, const float *correction, int n_groups, int keep,
+                       int group_top, bool renormalize, float norm_eps, float route_scale, int *chosen, float *weight, cudaStream_t s);
+// out[t, :] = x[t, :] * sigmoid(gate[t * gate_stride]), 32-bit rows
+void row_gate(const float *x, float *out, const float *gate, long long gate_stride, int n_rows, int cols, cudaStream_t s);
 int moe_tile_rows();
 void moe_sort(const int *chosen, int n_rows, int n_experts, int tile_rows, int *offsets, int *perm, int *tiles, cudaStream_t s);
 // x [T, width]; up [E, ff, width], down [E, width, ff] in x's type; out [top, T, width] 32-bit.  `gated`: up is

@@ -97,7 +97,8 @@ LLM_EXPORT int llm_latent_rotate_q(const float *q, long long ldq, void *out, lon
 // One CTA takes 128 query rows of one head of one sequence, its eight warps 16 rows each; key tiles of 64 rows are
 // walked with two tiles in flight, up to the one that holds the CTA's last row; a warp sits out the tiles that lie
 // wholly behind its rows.  q [T, heads * (d + rot)] (rotated), kv [T, heads * d | heads * dv], kr [T, rot]
-// (rotated), out [T, heads * dv]; sequence b owns rows seq_start[b] .. seq_start[b+1]-1 at positions 0 .. .
+// (rotated), out [T, heads * dv]; sequence b owns rows seq_start[b] .. seq_start[b+1]-1 at positions 0 .. ; with
+// `window` > 0 the row at position p sees keys p - window + 1 .. p only.
 // Key rows are d + rot channels rounded up to 16 (the rest zeros), value rows DVP >= dv channels (the rest zeros).
 constexpr int LP_WARPS = 8;
 constexpr int LP_BM = 16 * LP_WARPS;
@@ -106,7 +107,7 @@ template <int DVP>
 __global__ void __launch_bounds__(LP_WARPS * 32)
 latent_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long ldq, const __nv_bfloat16 *__restrict__ kv, long long ldkv,
                       const __nv_bfloat16 *__restrict__ kr, __nv_bfloat16 *__restrict__ out, long long ldo,
-                      const int *__restrict__ seq_start, int n_heads, int d, int rot, int dv, float scale_log2) {
+                      const int *__restrict__ seq_start, int n_heads, int d, int rot, int dv, float scale_log2, int window) {
   constexpr int LDV = DVP + 8;
   constexpr int VCH = DVP / 8;
   constexpr int NT = LT_BN / 8;
@@ -131,7 +132,8 @@ latent_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long ldq, const 
   const int rows = min(LP_BM, n_q - r0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int n_iter = min((n_q + LT_BN - 1) / LT_BN, (r0 + LP_BM) / LT_BN);   // key tiles 0 .. the one with the CTA's last row
+  const int n_iter = min((n_q + LT_BN - 1) / LT_BN, (r0 + LP_BM) / LT_BN);   // key tiles up to the one with the CTA's last row,
+  const int it0 = window > 0 ? max(0, r0 - window + 1) / LT_BN : 0;          // from the one with the first key its first row sees
   const int d8 = d / 8, dk8 = dk / 8, dv8 = dv / 8;
   const size_t v_off = (size_t)n_heads * d + (size_t)h * dv;
 
@@ -159,7 +161,7 @@ latent_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long ldq, const 
     const bool ok = r < rows && ch < dk8;
     cp_async16(sQ + r * ldk + ch * 8, ok ? q + (size_t)(q0 + r0 + r) * ldq + (size_t)h * dk + ch * 8 : q, ok);
   }
-  load_kv(0, 0);
+  load_kv(it0, 0);
   cp_async_commit();
 
   float o[DT][4];
@@ -170,15 +172,16 @@ latent_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long ldq, const 
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int pos0 = r0 + warp * 16 + g, pos1 = pos0 + 8;
 
-  for (int it = 0; it < n_iter; ++it) {
-    const int stage = it & 1;
+  for (int it = it0; it < n_iter; ++it) {
+    const int stage = (it - it0) & 1;
     if (it + 1 < n_iter) load_kv(it + 1, stage ^ 1);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
     const __nv_bfloat16 *tk = sK + stage * LT_BN * ldk, *tv = sV + stage * LT_BN * LDV;
     const int k0 = it * LT_BN;
-    if (k0 <= r0 + warp * 16 + 15) {                         // else: no row of this warp sees a key of the tile
+    // else: no row of this warp sees a key of the tile (it lies behind the rows, or before the first row's window)
+    if (k0 <= r0 + warp * 16 + 15 && (window == 0 || k0 + LT_BN - 1 > r0 + warp * 16 - window)) {
 
     float s[NT][4];
 #pragma unroll
@@ -205,6 +208,15 @@ latent_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long ldq, const 
         for (int j = 0; j < 4; ++j) {
           const int key = k0 + n * 8 + 2 * t + (j & 1);
           if (key > ((j & 2) ? pos1 : pos0)) s[n][j] = -INFINITY;
+        }
+    }
+    if (window > 0 && k0 <= r0 + warp * 16 + 15 - window) {  // a tile on the window's edge: the row at p sees key j when j > p - window
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int key = k0 + n * 8 + 2 * t + (j & 1);
+          if (key <= ((j & 2) ? pos1 : pos0) - window) s[n][j] = -INFINITY;
         }
     }
 
@@ -297,37 +309,38 @@ LLM_EXPORT int llm_latent_prefill_supports(int d, int rot, int dv) {
 template <int DVP>
 static int launch_latent_prefill(const void *q, long long ldq, const void *kv, long long ldkv, const void *kr, void *out, long long ldo,
                                  const int *seq_start, int n_seqs, int max_q_len, int n_heads, int d, int rot, int dv, float scale,
-                                 cudaStream_t stream) {
+                                 int window, cudaStream_t stream) {
   const size_t smem = latent_prefill_smem(d, rot, DVP);
   auto kern = latent_prefill_kernel<DVP>;
   LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "latent_prefill attribute");
   dim3 grid((max_q_len + LP_BM - 1) / LP_BM, n_heads, n_seqs);
   llm_launch(kern, grid, dim3(LP_WARPS * 32), smem, stream, (const __nv_bfloat16 *)q, ldq, (const __nv_bfloat16 *)kv, ldkv,
-             (const __nv_bfloat16 *)kr, (__nv_bfloat16 *)out, ldo, seq_start, n_heads, d, rot, dv, scale * 1.4426950408889634f);
+             (const __nv_bfloat16 *)kr, (__nv_bfloat16 *)out, ldo, seq_start, n_heads, d, rot, dv, scale * 1.4426950408889634f, window);
   LLM_CHECK_LAUNCH("latent_prefill");
   return LLM_OK;
 }
 
 LLM_EXPORT int llm_latent_prefill(const void *q, long long ldq, const void *kv, long long ldkv, const void *kr, void *out, long long ldo,
                                   const int *seq_start, int n_seqs, int max_q_len, int n_heads, int d, int rot, int dv, float scale,
-                                  cudaStream_t stream) {
+                                  int window, cudaStream_t stream) {
   if (n_seqs == 0 || max_q_len == 0) return LLM_OK;
+  LLM_REQUIRE(window >= 0, "latent_prefill: bad window");
   LLM_REQUIRE(llm_latent_prefill_supports(d, rot, dv), "latent_prefill: heads of %d + %d key and %d value channels are not supported", d,
               rot, dv);
   LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_heads > 0 && n_heads <= 65535 && ldq % 8 == 0 && ldkv % 8 == 0 && ldo % 2 == 0 &&
                   (rot == 0 || kr),
               "latent_prefill: bad sizes");
   switch (latent_dvp(dv)) {
-    case 32: return launch_latent_prefill<32>(q, ldq, kv, ldkv, kr, out, ldo, seq_start, n_seqs, max_q_len, n_heads, d, rot, dv, scale, stream);
-    case 64: return launch_latent_prefill<64>(q, ldq, kv, ldkv, kr, out, ldo, seq_start, n_seqs, max_q_len, n_heads, d, rot, dv, scale, stream);
-    case 128: return launch_latent_prefill<128>(q, ldq, kv, ldkv, kr, out, ldo, seq_start, n_seqs, max_q_len, n_heads, d, rot, dv, scale, stream);
-    default: return launch_latent_prefill<256>(q, ldq, kv, ldkv, kr, out, ldo, seq_start, n_seqs, max_q_len, n_heads, d, rot, dv, scale, stream);
+    case 32: return launch_latent_prefill<32>(q, ldq, kv, ldkv, kr, out, ldo, seq_start, n_seqs, max_q_len, n_heads, d, rot, dv, scale, window, stream);
+    case 64: return launch_latent_prefill<64>(q, ldq, kv, ldkv, kr, out, ldo, seq_start, n_seqs, max_q_len, n_heads, d, rot, dv, scale, window, stream);
+    case 128: return launch_latent_prefill<128>(q, ldq, kv, ldkv, kr, out, ldo, seq_start, n_seqs, max_q_len, n_heads, d, rot, dv, scale, window, stream);
+    default: return launch_latent_prefill<256>(q, ldq, kv, ldkv, kr, out, ldo, seq_start, n_seqs, max_q_len, n_heads, d, rot, dv, scale, window, stream);
   }
 }
 
 // ---------------------------------------------------------------- every other step: all heads over the cached rows
 // qa [T, heads * row] = [W_uk^T q_unrotated | rotated q part] per head (latent_absorb), cache [pages, page_size, row];
-// token t of sequence tok_seq[t] sees positions 0 .. tok_pos[t].  Result per head: the weighted sum of the rows'
+// token t of sequence tok_seq[t] sees positions 0 .. tok_pos[t], or with `window` > 0 the last `window` of them.  Result per head: the weighted sum of the rows'
 // first kv_rank channels, out [T, heads * kv_rank] (n_splits == 1) or unnormalised partial sums ws_o
 // [T, heads, n_splits, kv_rank] with (maximum in the exponent's units, sum) in ws_ml [T, heads, n_splits, 2].
 constexpr int LD_WARPS = 8;
@@ -341,7 +354,7 @@ __global__ void __launch_bounds__(LD_WARPS * 32)
 latent_decode_kernel(const __nv_bfloat16 *__restrict__ qa, long long ldq, const __nv_bfloat16 *__restrict__ cache, int page_size,
                      const int *__restrict__ tok_seq, const int *__restrict__ tok_pos, const int *__restrict__ page_table, int pt_stride,
                      int n_heads, int row, int kv_rank, int n_splits, float scale_log2, __nv_bfloat16 *__restrict__ out, long long ldo,
-                     float *__restrict__ ws_o, float *__restrict__ ws_ml) {
+                     float *__restrict__ ws_o, float *__restrict__ ws_ml, int window) {
   constexpr int SL = MAXR / 4;           // value channels of a warp
   constexpr int DT = SL / 8;
   constexpr int NT = LT_BN / 8;
@@ -359,9 +372,10 @@ latent_decode_kernel(const __nv_bfloat16 *__restrict__ qa, long long ldq, const 
   const int hg = warp >> 2, part = warp & 3;       // head group; key quarter in the first product, channel quarter in the second
   const int pos = tok_pos[tok], len = pos + 1;
   const int *pt = page_table + (size_t)tok_seq[tok] * pt_stride;
-  const int tiles = (len + LT_BN - 1) / LT_BN;
+  const int kstart = window > 0 ? max(0, pos - window + 1) : 0;      // the first key the token sees
+  const int tile_first = kstart / LT_BN, tiles = (len + LT_BN - 1) / LT_BN - tile_first;
   const int per = (tiles + n_splits - 1) / n_splits;
-  const int kt0 = split * per, kt1 = min(tiles, kt0 + per);
+  const int kt0 = tile_first + split * per, kt1 = min(tile_first + tiles, kt0 + per);
   const int n_iter = kt1 - kt0;
   const int head_a = h0 + hg * 16 + g, head_b = head_a + 8;
 
@@ -384,8 +398,8 @@ latent_decode_kernel(const __nv_bfloat16 *__restrict__ qa, long long ldq, const 
     for (int c = tid; c < LT_BN * rch; c += LD_WARPS * 32) {
       const int r = c / rch, ch = c - r * rch;
       const int j = kt * LT_BN + r;
-      const bool ok = j < len && ch < row8;
-      const int jj = j < len ? j : 0;
+      const bool ok = j >= kstart && j < len && ch < row8;
+      const int jj = j >= kstart && j < len ? j : pos;       // a page before the window may have been given back
       const __nv_bfloat16 *src = cache + ((size_t)pt[jj / page_size] * page_size + jj % page_size) * (size_t)row + (ok ? ch : 0) * 8;
       cp_async16(tk + r * ldr + ch * 8, src, ok);
     }
@@ -438,10 +452,11 @@ latent_decode_kernel(const __nv_bfloat16 *__restrict__ qa, long long ldq, const 
       const float2 a = *reinterpret_cast<const float2 *>(sS + (hg * 16 + g) * LD_SS + n * 8 + 2 * t);
       const float2 b = *reinterpret_cast<const float2 *>(sS + (hg * 16 + g + 8) * LD_SS + n * 8 + 2 * t);
       const int key = k0 + n * 8 + 2 * t;
-      s[n][0] = key <= pos ? a.x : -INFINITY;
-      s[n][1] = key + 1 <= pos ? a.y : -INFINITY;
-      s[n][2] = key <= pos ? b.x : -INFINITY;
-      s[n][3] = key + 1 <= pos ? b.y : -INFINITY;
+      const bool see0 = key <= pos && key >= kstart, see1 = key + 1 <= pos && key + 1 >= kstart;
+      s[n][0] = see0 ? a.x : -INFINITY;
+      s[n][1] = see1 ? a.y : -INFINITY;
+      s[n][2] = see0 ? b.x : -INFINITY;
+      s[n][3] = see1 ? b.y : -INFINITY;
     }
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -599,22 +614,23 @@ LLM_EXPORT long long llm_latent_decode_floats_needed(int n_tokens, int n_heads, 
 template <int MAXR>
 static int launch_latent_decode(const void *qa, long long ldq, const void *cache, int page_size, const int *tok_seq, const int *tok_pos,
                                 const int *page_table, int pt_stride, int n_tokens, int n_heads, int row, int kv_rank, int n_splits,
-                                float scale, void *out, long long ldo, float *ws_o, float *ws_ml, cudaStream_t stream) {
+                                float scale, void *out, long long ldo, float *ws_o, float *ws_ml, int window, cudaStream_t stream) {
   const size_t smem = latent_decode_smem(row);
   auto kern = latent_decode_kernel<MAXR>;
   LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "latent_decode attribute");
   dim3 grid(n_splits, (n_heads + LD_HT - 1) / LD_HT, n_tokens);
   llm_launch(kern, grid, dim3(LD_WARPS * 32), smem, stream, (const __nv_bfloat16 *)qa, ldq, (const __nv_bfloat16 *)cache, page_size,
              tok_seq, tok_pos, page_table, pt_stride, n_heads, row, kv_rank, n_splits, scale * 1.4426950408889634f, (__nv_bfloat16 *)out,
-             ldo, ws_o, ws_ml);
+             ldo, ws_o, ws_ml, window);
   LLM_CHECK_LAUNCH("latent_decode");
   return LLM_OK;
 }
 
 LLM_EXPORT int llm_latent_decode(const void *qa, long long ldq, const void *cache, int page_size, const int *tok_seq, const int *tok_pos,
                                  const int *page_table, int pt_stride, int n_tokens, int n_heads, int kv_rank, int rot, int n_splits,
-                                 float scale, void *out, long long ldo, float *ws, cudaStream_t stream) {
+                                 float scale, void *out, long long ldo, float *ws, int window, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(window >= 0, "latent_decode: bad window");
   LLM_REQUIRE(llm_latent_decode_supports(kv_rank, rot), "latent_decode: rows of %d + %d channels are not supported", kv_rank, rot);
   LLM_REQUIRE(n_tokens > 0 && n_tokens <= 65535 && n_heads > 0 && page_size > 0 && n_splits >= 1 && n_splits <= LJ_MAX && ldq % 8 == 0 && ldo % 2 == 0 &&
                   (n_splits == 1 || ws),
@@ -623,9 +639,9 @@ LLM_EXPORT int llm_latent_decode(const void *qa, long long ldq, const void *cach
   float *ws_o = ws, *ws_ml = ws ? ws + (size_t)n_tokens * n_heads * n_splits * kv_rank : nullptr;
   int st;
   switch (latent_maxr(kv_rank)) {
-    case 128: st = launch_latent_decode<128>(qa, ldq, cache, page_size, tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, row, kv_rank, n_splits, scale, out, ldo, ws_o, ws_ml, stream); break;
-    case 256: st = launch_latent_decode<256>(qa, ldq, cache, page_size, tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, row, kv_rank, n_splits, scale, out, ldo, ws_o, ws_ml, stream); break;
-    default: st = launch_latent_decode<512>(qa, ldq, cache, page_size, tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, row, kv_rank, n_splits, scale, out, ldo, ws_o, ws_ml, stream); break;
+    case 128: st = launch_latent_decode<128>(qa, ldq, cache, page_size, tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, row, kv_rank, n_splits, scale, out, ldo, ws_o, ws_ml, window, stream); break;
+    case 256: st = launch_latent_decode<256>(qa, ldq, cache, page_size, tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, row, kv_rank, n_splits, scale, out, ldo, ws_o, ws_ml, window, stream); break;
+    default: st = launch_latent_decode<512>(qa, ldq, cache, page_size, tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, row, kv_rank, n_splits, scale, out, ldo, ws_o, ws_ml, window, stream); break;
   }
   if (st != LLM_OK || n_splits == 1) return st;
   llm_launch(latent_join_kernel, dim3(n_heads, n_tokens), dim3(128), 0, stream, (const float *)ws_o, (const float *)ws_ml, n_splits, kv_rank,

@@ -106,6 +106,167 @@ LLM_EXPORT int llm_moe_route(const float *logits, long long ld, int n_tokens, in
   return LLM_OK;
 }
 
+// ---------------------------------------------------------------- choice among the best groups, by corrected scores
+// One warp per token.  Scores s = sigmoid(z) (score_kind 0) or softmax(z) (1).  The CHOICE is made on c = s +
+// correction (a vector over the experts; null: c = s); the WEIGHTS are the chosen experts' s.  With n_groups > 1
+// the experts form n_groups equal groups of neighbours, a group's score is the sum of its `group_top` largest c,
+// and only experts of the `keep` best groups can be chosen: the others' c count as minus infinity (c may be
+// negative, so nought would not do).  Weights: s, or with `renormalize` s / (sum of the chosen s + norm_eps), then
+// times route_scale.  Ties go to the lower index.  Everything is 32-bit; a token's result depends on its row alone.
+__global__ void moe_route_grouped_kernel(const float *__restrict__ logits, long long ld, int n_tokens, int n_experts, int top,
+                                         int score_kind, const float *__restrict__ correction, int n_groups, int keep,
+                                         int group_top, int renormalize, float norm_eps, float route_scale,
+                                         int *__restrict__ chosen, float *__restrict__ weight) {
+  extern __shared__ float route_sh[];            // per warp: c [E], group scores [n_groups]
+  grid_dependents_launch();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= n_tokens) return;
+  float *c = route_sh + (size_t)warp * (n_experts + n_groups), *gs = c + n_experts;
+  const float *z = logits + (size_t)t * ld;
+  float zmax = -INFINITY, denom = 1.f;
+  if (score_kind == 1) {
+    for (int e = lane; e < n_experts; e += 32) zmax = fmaxf(zmax, z[e]);
+    zmax = warp_max(zmax);
+    float s = 0.f;
+    for (int e = lane; e < n_experts; e += 32) s += expf(z[e] - zmax);
+    denom = warp_sum(s);
+  }
+  auto score_of = [&](int e) { return score_kind == 1 ? expf(z[e] - zmax) / denom : 1.f / (1.f + expf(-z[e])); };
+  for (int e = lane; e < n_experts; e += 32) c[e] = score_of(e) + (correction ? correction[e] : 0.f);
+  __syncwarp();
+  if (n_groups > 1) {
+    const int per = n_experts / n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+      // the sum of the group's group_top largest: each pass takes the largest below (value, index) of the pass before
+      float sum = 0.f, last_v = INFINITY;
+      int last_e = -1;
+      for (int k = 0; k < group_top && k < per; ++k) {
+        float best = -INFINITY;
+        int best_e = -1;
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+          const float v = c[e];
+          const bool after = v < last_v || (v == last_v && e > last_e);
+          if (after && (best_e < 0 || v > best)) {
+            best = v;
+            best_e = e;
+          }
+        }
+        sum += best;
+        last_v = best;
+        last_e = best_e;
+      }
+      gs[g] = sum;
+    }
+    __syncwarp();
+    // the `keep` best groups, one after another; a kept group's score becomes +infinity as its mark
+    for (int k = 0; k < keep; ++k) {
+      float best = -INFINITY;
+      int best_g = 0x7fffffff;
+      for (int g = lane; g < n_groups; g += 32) {
+        const float v = gs[g];
+        if (v != INFINITY && (best_g == 0x7fffffff || v > best)) {
+          best = v;
+          best_g = g;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+        if (og != 0x7fffffff && (best_g == 0x7fffffff || ob > best || (ob == best && og < best_g))) {
+          best = ob;
+          best_g = og;
+        }
+      }
+      __syncwarp();
+      if (lane == 0 && best_g != 0x7fffffff) gs[best_g] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < n_experts; e += 32)
+      if (gs[e / per] != INFINITY) c[e] = -INFINITY;
+    __syncwarp();
+  }
+  float total = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int e = lane; e < n_experts; e += 32) {
+      const float v = c[e];
+      if (v != -INFINITY && (best_e == 0x7fffffff || v > best)) {
+        best = v;
+        best_e = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (oe != 0x7fffffff && (best_e == 0x7fffffff || ob > best || (ob == best && oe < best_e))) {
+        best = ob;
+        best_e = oe;
+      }
+    }
+    __syncwarp();
+    if (best_e == 0x7fffffff) best_e = 0;          // fewer experts may be chosen than `top`: refused by the caller
+    const float s = score_of(best_e);
+    total += s;
+    if (lane == 0) {
+      c[best_e] = -INFINITY;
+      chosen[(size_t)t * top + j] = best_e;
+      weight[(size_t)t * top + j] = s;
+    }
+    __syncwarp();
+  }
+  for (int j = lane; j < top; j += 32) {
+    float w = weight[(size_t)t * top + j];
+    if (renormalize) w = w / (total + norm_eps);
+    weight[(size_t)t * top + j] = w * route_scale;
+  }
+}
+
+LLM_EXPORT int llm_moe_route_grouped(const float *logits, long long ld, int n_tokens, int n_experts, int top, int score_kind,
+                                     const float *correction, int n_groups, int keep, int group_top, int renormalize, float norm_eps,
+                                     float route_scale, int *chosen, float *weight, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && n_experts > 0 && top > 0 && top <= n_experts, "moe_route: %d of %d experts", top, n_experts);
+  LLM_REQUIRE(n_experts <= 2048, "moe_route: at most 2048 experts (%d)", n_experts);
+  LLM_REQUIRE(score_kind == 0 || score_kind == 1, "moe_route: unknown score %d", score_kind);
+  LLM_REQUIRE(n_groups >= 1 && n_experts % n_groups == 0 && keep >= 1 && keep <= n_groups && group_top >= 1,
+              "moe_route: %d experts in %d groups of which %d are kept", n_experts, n_groups, keep);
+  LLM_REQUIRE(n_groups == 1 || (long long)keep * (n_experts / n_groups) >= top, "moe_route: %d kept groups of %d experts hold fewer than the %d to choose",
+              keep, n_experts / n_groups, top);
+  const int warps = 4;
+  const size_t smem = (size_t)warps * (size_t)(n_experts + n_groups) * sizeof(float);
+  llm_launch(moe_route_grouped_kernel, dim3((n_tokens + warps - 1) / warps), dim3(warps * 32), smem, stream, logits, ld, n_tokens,
+             n_experts, top, score_kind, correction, n_groups, keep, group_top, renormalize, norm_eps, route_scale, chosen, weight);
+  LLM_CHECK_LAUNCH("moe_route_grouped");
+  return LLM_OK;
+}
+
+// out[t, :] = x[t, :] * sigmoid(gate[t * gate_stride]) (32-bit rows): a feed-forward's result weighed by one number per token.
+__global__ void row_gate_kernel(const float *__restrict__ x, float *__restrict__ out, const float *__restrict__ gate,
+                                long long gate_stride, int cols, long long total) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / cols;
+    out[i] = x[i] * (1.f / (1.f + expf(-gate[t * gate_stride])));
+  }
+}
+LLM_EXPORT int llm_row_gate(const float *x, float *out, const float *gate, long long gate_stride, int n_rows, int cols,
+                            cudaStream_t stream) {
+  if (n_rows == 0 || cols == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && cols > 0 && x && out && gate, "row_gate: bad arguments");
+  const long long total = (long long)n_rows * cols;
+  long long blocks = (total + 255) / 256;
+  if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+  llm_launch(row_gate_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, out, gate, gate_stride, cols, total);
+  LLM_CHECK_LAUNCH("row_gate");
+  return LLM_OK;
+}
+
 // ---------------------------------------------------------------- rows by expert
 // One CTA.  offsets[e] .. offsets[e + 1]: the sorted places of expert e's rows; perm[place] = row;
 // tiles[0] = number of row tiles, then (expert, first place) per tile of at most `tile_rows` rows of

@@ -571,3 +571,104 @@ LLM_EXPORT int llm_rope_pairs_place(int in_dtype, int dtype, const void *qkv, lo
   LLM_CHECK_LAUNCH("rope_pairs_place");
   return LLM_OK;
 }
+
+// ---------------------------------------------------------------- rotation, then a unit norm per head, + append
+// For mixers that divide every query and key head by its root mean square AFTER the rotation (no weight):
+//   rotation of the first rot_dim channels of every q and k head (pairs i, i + rot_dim/2; the table's row may
+//   carry a factor on cosines and sines alike), then head <- head / sqrt(mean(head^2) + eps) over its d channels
+//   (eps < 0: no norm), q -> q_out, k and v -> the token's row of the paged cache; values of width dv as they are.
+// A row of the stacked product is [q: n_heads * d | k: n_kv * d | v: n_kv * dv | anything else].  One CTA per
+// token, a warp per head in turn; a head's channels stay in registers between the rotation and the norm
+// (d <= 512).  Angles come from the table (computed in 64-bit, rounded once); sums and factors are 32-bit and
+// a head's sum has a fixed order.
+constexpr int HN_MAX_ITEMS = 16;          // items of a lane: d - rot_dim/2 <= 32 * HN_MAX_ITEMS
+template <typename TI, typename T>
+__global__ void __launch_bounds__(256)
+rope_headnorm_place_kernel(const TI *__restrict__ qkv, long long row_stride, T *__restrict__ q_out, long long q_stride, int n_heads,
+                           int n_kv, int d, int dv, float eps, const float *__restrict__ table, int table_rows, int rot_dim,
+                           const int *__restrict__ tok_seq, const int *__restrict__ tok_pos, const int *__restrict__ page_table,
+                           int pt_stride, T *__restrict__ kcache, T *__restrict__ vcache, int page_size, int write_cache) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pos = tok_pos[t];
+  const TI *row = qkv + (size_t)t * row_stride;
+  const int qw = n_heads * d, kw = n_kv * d;
+  size_t cache_row = 0;
+  if (write_cache) {
+    const int page = page_table[(size_t)tok_seq[t] * pt_stride + pos / page_size];
+    cache_row = (size_t)page * n_kv * page_size + (pos % page_size);
+  }
+  const int half = rot_dim / 2;
+  const float *cs = table ? table + (size_t)(pos < table_rows ? pos : table_rows - 1) * rot_dim : nullptr;
+  const int per_head = d - half;               // `half` pairs, then the channels that are not rotated
+  const int n_slots = n_heads + (write_cache ? n_kv : 0);
+  for (int slot = warp; slot < n_slots; slot += 8) {
+    const bool is_q = slot < n_heads;
+    const TI *src = row + (size_t)slot * d;
+    T *dst = is_q ? q_out + (size_t)t * q_stride + (size_t)slot * d : kcache + (cache_row + (size_t)(slot - n_heads) * page_size) * d;
+    float a[HN_MAX_ITEMS], b[HN_MAX_ITEMS];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < HN_MAX_ITEMS; ++k) {
+      const int i = lane + 32 * k;
+      a[k] = b[k] = 0.f;
+      if (i < per_head) {
+        if (i < half) {
+          const float u = to_float(src[i]), v = to_float(src[i + half]);
+          const float c = cs[i], s = cs[half + i];
+          a[k] = u * c - v * s;
+          b[k] = v * c + u * s;
+        } else {
+          a[k] = to_float(src[i + half]);
+        }
+        ss = fmaf(a[k], a[k], ss);
+        ss = fmaf(b[k], b[k], ss);
+      }
+    }
+    float fac = 1.f;
+    if (eps >= 0.f) fac = 1.f / sqrtf(warp_sum(ss) / (float)d + eps);
+#pragma unroll
+    for (int k = 0; k < HN_MAX_ITEMS; ++k) {
+      const int i = lane + 32 * k;
+      if (i < per_head) {
+        if (i < half) {
+          dst[i] = from_float<T>(a[k] * fac);
+          dst[i + half] = from_float<T>(b[k] * fac);
+        } else {
+          dst[i + half] = from_float<T>(a[k] * fac);
+        }
+      }
+    }
+  }
+  if (write_cache) {
+    const TI *vsrc = row + qw + kw;
+    for (int item = threadIdx.x; item < n_kv * dv; item += 256) {
+      const int kvh = item / dv, ch = item - kvh * dv;
+      vcache[(cache_row + (size_t)kvh * page_size) * dv + ch] = from_float<T>(to_float(vsrc[item]));
+    }
+  }
+}
+
+LLM_EXPORT int llm_rope_headnorm_place(int in_dtype, int dtype, const void *qkv, long long row_stride, void *q_out, long long q_stride,
+                                       int n_tokens, int n_heads, int n_kv, int d, int dv, float eps, const float *table, int table_rows,
+                                       int rot_dim, const int *tok_seq, const int *tok_pos, const int *page_table, int pt_stride,
+                                       void *kcache, void *vcache, int page_size, int write_cache, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && d > 0 && dv > 0, "rope_headnorm_place: bad sizes");
+  LLM_REQUIRE(rot_dim % 2 == 0 && rot_dim <= d && rot_dim >= 0 && (rot_dim == 0 || table != nullptr),
+              "rope_headnorm_place: rotated width %d does not fit head size %d", rot_dim, d);
+  LLM_REQUIRE(d - rot_dim / 2 <= 32 * HN_MAX_ITEMS, "rope_headnorm_place: heads of %d channels are not supported", d);
+  LLM_REQUIRE(row_stride >= (long long)n_heads * d + (long long)n_kv * (d + dv), "rope_headnorm_place: the stacked rows are too short");
+#define HN_PLACE(TI, T)                                                                                                       \
+  llm_launch(rope_headnorm_place_kernel<TI, T>, dim3(n_tokens), dim3(256), 0, stream, (const TI *)qkv, row_stride, (T *)q_out, \
+             q_stride, n_heads, n_kv, d, dv, eps, table, table_rows, rot_dim, tok_seq, tok_pos, page_table, pt_stride,       \
+             (T *)kcache, (T *)vcache, page_size, write_cache)
+  if (in_dtype == LLM_F32 && dtype == LLM_F32) HN_PLACE(float, float);
+  else if (in_dtype == LLM_F32 && dtype == LLM_BF16) HN_PLACE(float, __nv_bfloat16);
+  else if (in_dtype == LLM_BF16 && dtype == LLM_BF16) HN_PLACE(__nv_bfloat16, __nv_bfloat16);
+  else LLM_FAIL("rope_headnorm_place: unsupported dtypes in %d out %d", in_dtype, dtype);
+#undef HN_PLACE
+  LLM_CHECK_LAUNCH("rope_headnorm_place");
+  return LLM_OK;
+}

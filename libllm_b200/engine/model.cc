@@ -25,8 +25,8 @@ DType parse_dtype(const std::string &name) {
 
 RandomLaw random_law(const TensorNeed &need, float std) {
   const bool is_bias = need.name.size() >= 4 && need.name.compare(need.name.size() - 4, 4, "bias") == 0;
-  if (need.role == TensorRole::Vector && !is_bias) return {1, 0.9f, 1.1f};
-  return {0, 0.f, std};
+  if (need.role == TensorRole::Vector && !is_bias) return {1, 0.9f * need.drawn_scale, 1.1f * need.drawn_scale};
+  return {0, 0.f, std * need.drawn_scale};
 }
 
 namespace {
@@ -70,6 +70,10 @@ Model::Model(ModelSpec spec, Json config, DType dtype, int64_t max_positions, in
   env_.page_size = page_size;
   env_.shared = &shared_;
   for (const auto &l : spec_.layers) layers_.push_back(build_as<Block>("block", l, env_));
+  if (spec_.streams < 1) LLM_THROW(Config, "a model has at least one residual stream (%d)", spec_.streams);
+  for (size_t i = 0; i < layers_.size(); ++i)
+    if (layers_[i]->streams() != spec_.streams)
+      LLM_THROW(Config, "layer %zu works on %d copies of the residual stream, the model carries %d", i, layers_[i]->streams(), spec_.streams);
   final_norm_ = build_as<Norm>("norm", spec_.final_norm, env_);
   for (size_t i = 0; i < spec_.schedule.size(); ++i) {
     const ScheduleEntry &e = spec_.schedule[i];
@@ -77,6 +81,7 @@ Model::Model(ModelSpec spec, Json config, DType dtype, int64_t max_positions, in
       LLM_THROW(Config, "schedule entry %zu names layer %d, the model has %zu", i, e.layer, layers_.size());
     if (e.cache_from >= (int)i)
       LLM_THROW(Config, "schedule entry %zu reads the cache of entry %d, which does not run before it", i, e.cache_from);
+    if (!e.input_mix.empty() && spec_.streams > 1) LLM_THROW(Unsupported, "an input mix goes with one residual stream");
     if (!e.input_mix.empty()) input_mixes_[e.input_mix];
   }
 }
@@ -177,7 +182,8 @@ Act Model::forward(StepContext &ctx, KVCache &cache, const std::vector<const int
                    const int *fed_tokens, const int *fed_rows) {
   if (!loaded_) LLM_THROW(InvalidArg, "the model has no weights yet");
   const int64_t T = ctx.n_tokens, H = spec_.hidden;
-  float *resid = ctx.arena->alloc_n<float>((size_t)(T * H));
+  // several copies of the stream lie one behind the other; the token rows go to the first, the others are equal to it
+  float *resid = ctx.arena->alloc_n<float>((size_t)(T * H) * (size_t)spec_.streams);
   kernels::embedding(embedding_.dtype, embedding_.data(), ctx.tokens, fed_tokens, fed_rows, resid, (int)T, (int)H,
                      (int)spec_.vocab_size, ctx.stream, positions_.data(), (int)positions_.rows, ctx.tok_pos);
   if (spec_.embedding_scale != 1.0) kernels::scale_rows(resid, T * H, (float)spec_.embedding_scale, ctx.stream);
@@ -190,6 +196,9 @@ Act Model::forward(StepContext &ctx, KVCache &cache, const std::vector<const int
   stream.resid = resid;
   stream.rows = T;
   stream.hidden = H;
+  stream.streams = spec_.streams;
+  stream.stream_stride = T * H;
+  stream.spread = spec_.streams == 1;
   Arena *const step_arena = ctx.arena;
   for (size_t i = 0; i < spec_.schedule.size(); ++i) {
     const ScheduleEntry &e = spec_.schedule[i];
@@ -215,6 +224,20 @@ Act Model::forward(StepContext &ctx, KVCache &cache, const std::vector<const int
   }
   ctx.rows_read_after = nullptr;
   ctx.nothing_read_after = false;
+  if (stream.streams > 1) {
+    // the last norm reads the sum of the copies, at the wanted rows: the last sublayer's result is applied on the way
+    flush_chain(ctx);
+    const int64_t n = stream.picked ? stream.rows : ctx.n_want;
+    float *sum = ctx.arena->alloc_n<float>((size_t)(n * H));
+    kernels::hyper_mix_norm(stream.resid, stream.spread ? stream.stream_stride : 0, nullptr, 0, stream.streams,
+                            stream.pending.data ? &stream.pending : nullptr, stream.pending_mix, stream.pending_out, nullptr, nullptr, 0.f,
+                            sum, DType::F32, stream.picked ? nullptr : ctx.want_rows, (int)n, (int)H, ctx.stream);
+    stream = ResidualStream();
+    stream.resid = sum;
+    stream.rows = n;
+    stream.hidden = H;
+    stream.picked = true;
+  }
   Act h = stream.picked ? final_norm_->forward(ctx, stream) : final_norm_->forward(ctx, stream, ctx.want_rows, ctx.n_want);
   Act logits = linear(ctx, h, *head_, nullptr, DType::F32);
   flush_chain(ctx);

@@ -17,7 +17,7 @@ ConfigReader reader_of(const Json &spec, const char *what) { return ConfigReader
 
 // ---------------------------------------------------------------- RMSNorm
 // y = x * w / sqrt(mean(x^2) + eps), sums and scaling in 32-bit (src/flint/cpu/normalizations.cc:52-64,
-// src/flint/cuda/rms_norm.cu:59-75).  Before the norm the stream's pending addition is applied in
+// src/flint/cuda/rms_norm.cu:59-75).  With `weight_offset` c the stored weight is applied as (c + w).  Before the norm the stream's pending addition is applied in
 // 32-bit: the reference's separate residual add (src/libllm/llama.cc:252-266).
 class RMSNorm : public Norm {
  public:
@@ -26,11 +26,22 @@ class RMSNorm : public Norm {
     size_ = r.integer("size");
     eps_ = r.number("eps");
     name_ = r.string("weight");
+    offset_ = r.number_or("weight_offset", 0.0, false);
   }
   std::vector<TensorNeed> tensor_needs() const override { return {{name_, {size_}, TensorRole::Vector, false}}; }
-  void load(const Loader &l) override { weight_ = l.fetch(tensor_needs()[0]); }
+  void load(const Loader &l) override {
+    weight_ = l.fetch(tensor_needs()[0]);
+    // a weight stored around nought and applied as (offset + w): added once, in 32-bit, to the 32-bit copy
+    if (offset_ != 0.0) kernels::add_scalar(weight_.buf.as<float>(), size_, (float)offset_, nullptr);
+  }
   std::vector<std::string> kernel_families() const override { return {"elementwise"}; }
+  bool rms_params(const float **weight, float *eps) const override {
+    *weight = weight_.buf.as<float>();
+    *eps = (float)eps_;
+    return true;
+  }
   Act forward(StepContext &ctx, ResidualStream &stream, const int *rows, int n_rows) override {
+    if (stream.streams > 1) LLM_THROW(InvalidArg, "rmsnorm: the residual stream has %d copies; the block that keeps them joins them first", stream.streams);
     const int64_t n = rows ? n_rows : stream.rows;
     Act out = ctx.arena->act(ctx.dtype, n, size_);
     if (ctx.chain && ctx.dtype == DType::BF16 &&
@@ -48,7 +59,7 @@ class RMSNorm : public Norm {
 
  private:
   int64_t size_;
-  double eps_;
+  double eps_, offset_ = 0.0;
   std::string name_;
   Weight weight_;
 };
@@ -256,6 +267,10 @@ class RotaryEmbedding : public PositionEncoding {
 //   values       "keys": there is no value matrix; a position's value is its key as projected (bias added), before
 //                the rotation.  Needs a rotation in neighbouring pairs (position.pairing "interleaved"), whose
 //                placement kernel also adds the biases (32-bit)
+//   head_norm    {eps}: AFTER the rotation every query head and every key head is divided by its root mean square over
+//                its head_dim channels, sqrt(mean + eps), without a weight (a rotation of pairs (i, i + rotary_dim/2) or none)
+//   null_key     a number s0: every query also sees one key whose score is s0 and which has no value, so that
+//                p_j = exp(s_j) / (exp(s0) + sum exp(s_j)); with 0 the softmax has one added to its denominator
 //   q_bias, k_bias, v_bias   names of the biases (default: the matrix's name with "weight" replaced by "bias").
 //                Without a rotation the biases are added where q, k and v are placed (32-bit), so that the
 //                product itself runs on the tensor cores like any other
@@ -295,11 +310,16 @@ class Attention : public Mixer {
     sink_ = (int)r.integer_or("sink", 0, 0);
     if (sink_ > 0 && (window_ == 0 || block_ > 0)) LLM_THROW(Config, "attention: kept first positions ('sink') go with a window");
     if (r.present("v_norm")) v_eps_ = (float)ConfigReader(r.object("v_norm"), "attention description: v_norm").number("eps", false);
+    if (r.present("head_norm")) head_eps_ = (float)ConfigReader(r.object("head_norm"), "attention description: head_norm").number("eps", false);
+    if (r.present("null_key")) null_score_ = (float)r.number("null_key", false);
     if (!spec.get("position").is_null()) position_ = build_as<PositionEncoding>("position", spec.get("position"), env);
     const Json &pos_spec = spec.get("position");
     pairs_place_ = position_ && pos_spec.is_object() && pos_spec.has("pairing") && pos_spec.get("pairing").is_string() &&
                    pos_spec.get("pairing").as_string() == "interleaved" && q_norm_name_.empty();
     place_adds_bias_ = (!position_ && q_norm_name_.empty()) || pairs_place_;
+    if (head_eps_ >= 0.f && (pairs_place_ || !q_norm_name_.empty() || bias_ || v_eps_ >= 0.f || values_from_keys_))
+      LLM_THROW(Unsupported, "attention: a norm per head after the rotation goes with a rotation of pairs (i, i + rotary_dim/2) or none, and with no other norm or bias");
+    if (head_eps_ >= 0.f) place_adds_bias_ = false;
     if (values_from_keys_ && (!pairs_place_ || dv_ != d_ || !gate_name_.empty() || v_eps_ >= 0.f))
       LLM_THROW(Unsupported, "attention: values that are the keys go with a rotation in neighbouring pairs, values as wide as keys, no gate and no value norm");
     if (v_eps_ >= 0.f && !place_adds_bias_) LLM_THROW(Unsupported, "attention: a value norm together with a rotation or a q/k norm is not built");
@@ -398,7 +418,8 @@ class Attention : public Mixer {
     const bool tiled = env_.page_size == 64 && d_ % 16 == 0 && d_ >= 16 && d_ <= 128;
     if (f.prefill_attention_tc && env_.page_size == 64 && (d_ == 64 || d_ == 128)) fams.push_back("attention_prefill_tc");
     else if (f.prefill_attention && tiled) fams.push_back("attention_prefill");
-    if (f.decode_attention_tc && tiled && group <= 16 && !bias_ && position_ && gate_name_.empty() && q_norm_name_.empty())
+    if (f.decode_attention_tc && tiled && group <= 16 && !bias_ && position_ && gate_name_.empty() && q_norm_name_.empty() &&
+        head_eps_ < 0.f && !(null_score_ > kernels::NO_NULL_KEY))
       fams.push_back("attention_decode_tc");
     else if (f.decode_attention && (d_ == 16 || d_ == 32 || d_ == 64 || d_ == 128) &&
              (group == 1 || group == 2 || group == 3 || group == 4 || group == 8))
@@ -430,7 +451,8 @@ class Attention : public Mixer {
     const float *table = position_ ? position_->half_split_table(&table_rows, &rot_dim) : nullptr;
     const bool has_gate = !gate_name_.empty();
     const float *gate = nullptr;
-    const bool fused = plain_ && !has_gate && q_norm_name_.empty() && table && !bias_ && ctx.decode_only && f.decode_attention_tc && ctx.dtype == DType::BF16 &&
+    const bool has_null = null_score_ > kernels::NO_NULL_KEY;
+    const bool fused = plain_ && !has_gate && q_norm_name_.empty() && head_eps_ < 0.f && !has_null && table && !bias_ && ctx.decode_only && f.decode_attention_tc && ctx.dtype == DType::BF16 &&
                        kernels::available("attention_decode_tc") && kernels::attention_decode_tc_supported(d_, cache->page_size, group);
     Act qkv = linear(ctx, x, w_qkv_, bias_ && !place_adds_bias_ ? b_qkv_.buf.as<float>() : nullptr, DType::F32, fused);
     flush_chain(ctx);
@@ -472,6 +494,10 @@ class Attention : public Mixer {
     } else if (place_adds_bias_ && (bias_ || v_eps_ >= 0.f)) {
       kernels::kv_place(qkv, q, n_heads_, n_kv_, d_, dv_, bias_ ? b_qkv_.buf.as<float>() : nullptr, v_eps_, ctx.tok_seq, ctx.tok_pos,
                         cache->page_table, cache->table_width, cache->k, cache->v, cache->page_size, cache->writes, ctx.stream);
+    } else if (head_eps_ >= 0.f) {
+      if (position_ && !table) LLM_THROW(Unsupported, "attention: a norm per head needs a position part with a half-split table (or none)");
+      kernels::rope_headnorm_place(qkv, q, n_heads_, n_kv_, d_, dv_, head_eps_, table, table_rows, rot_dim, ctx.tok_seq, ctx.tok_pos,
+                                   cache->page_table, cache->table_width, cache->k, cache->v, cache->page_size, cache->writes, ctx.stream);
     } else if (!q_norm_name_.empty() || dv_ != d_) {
       if (position_ && !table)
         LLM_THROW(Unsupported, "attention: a q/k norm or values of another width need a position part with a half-split table (or none)");
@@ -489,7 +515,7 @@ class Attention : public Mixer {
     // a gate per channel is applied behind the attention kernel, whichever it is
     const float *channel_gate = gate_per_channel_ ? gate : nullptr;
     if (gate_per_channel_) gate = nullptr;
-    if (ctx.dtype == DType::BF16 && plain_) {
+    if (ctx.dtype == DType::BF16 && plain_ && !has_null) {
       if (ctx.decode_only && f.decode_attention && kernels::available("attention_decode") &&
           kernels::attention_decode_supported(d_, group)) {
         // enough CTAs to fill the GPU about eight times over at the longest length, runs of at
@@ -530,7 +556,8 @@ class Attention : public Mixer {
     }
     if (!done)
       kernels::attention_generic(q, out, cache->k, cache->v, ctx.tok_seq, ctx.tok_pos, cache->page_table, cache->table_width,
-                                 n_heads_, n_kv_, d_, dv_, cache->page_size, window_, block_, scale_, gate, qkv.ld, ctx.stream, sink_);
+                                 n_heads_, n_kv_, d_, dv_, cache->page_size, window_, block_, scale_, gate, qkv.ld, ctx.stream, sink_, 0,
+                                 null_score_);
     if (channel_gate) kernels::head_gate(out, channel_gate, qkv.ld, n_heads_ * dv_, 1, ctx.stream);
     return linear(ctx, out, w_o_, nullptr, DType::F32, true);
   }
@@ -540,7 +567,7 @@ class Attention : public Mixer {
   int64_t gate_rows_ = 0;
   int n_heads_, n_kv_, d_, dv_, window_, block_, sink_ = 0;
   bool bias_, plain_, gate_per_channel_ = false, place_adds_bias_ = false, values_from_keys_ = false, pairs_place_ = false;
-  float scale_, qk_eps_ = 0.f, v_eps_ = -1.f;
+  float scale_, qk_eps_ = 0.f, v_eps_ = -1.f, head_eps_ = -1.f, null_score_ = kernels::NO_NULL_KEY;
   std::vector<std::string> bias_names_;
   std::string q_name_, k_name_, v_name_, o_name_, q_norm_name_, k_norm_name_, gate_name_;
   std::unique_ptr<PositionEncoding> position_;
@@ -767,6 +794,163 @@ class PreNormBlock : public Block {
   Weight conv_, mixer_scale_, ff_scale_;
 };
 
+// ---------------------------------------------------------------- pre-norm block over several residual streams
+// The model carries `streams` copies x_0 .. x_{S-1} of the residual stream, all equal to the token's row at the start
+// ("hyper-connections").  Sublayer q (the mixer, then the feed-forward) has a vector `in` [S], a vector `out` [S]
+// and a matrix `mix` [S, S] indexed [from, to]:
+//   u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_t <- sum_s mix[s, t] x_s + out[t] y   (all t at once, from the old x)
+// With in = out = (1), mix = (1) and one stream this is the pre-norm block.  A sublayer's result stays pending on the
+// stream with its `mix` and `out`; the next pass over the rows (the next sublayer's join and norm, or the model's
+// sum of the copies before its last norm) applies it, so a sublayer costs one pass over the S copies: read, move, join,
+// norm (csrc/elementwise.cu: hyper_mix_norm).  Everything between the sublayers is 32-bit.  The feed-forward may be
+// absent.  In the last layer of a step that wants few rows, the feed-forward runs for those rows alone.  With one
+// stream the three tensors may be missing from the files: they count as 1.
+class HyperBlock : public Block {
+ public:
+  HyperBlock(const Json &spec, const BuildEnv &env) : Block(spec, env) {
+    ConfigReader r = reader_of(spec, "hyper block");
+    streams_ = (int)r.integer("streams");
+    hidden_ = r.integer("hidden");
+    if (streams_ > 8) LLM_THROW(Unsupported, "hyper block: %d residual streams are not supported (up to 8)", streams_);
+    mixer_norm_ = build_as<Norm>("norm", r.object("mixer_norm"), env);
+    mixer_ = build_as<Mixer>("mixer", r.object("mixer"), env);
+    for (const char *k : {"mixer_in", "mixer_out", "mixer_mix"}) names_.push_back(r.string(k));
+    if (r.present("ff")) {
+      ff_norm_ = build_as<Norm>("norm", r.object("ff_norm"), env);
+      ff_ = build_as<FeedForward>("feed_forward", r.object("ff"), env);
+      for (const char *k : {"ff_in", "ff_out", "ff_mix"}) names_.push_back(r.string(k));
+    }
+  }
+  int streams() const override { return streams_; }
+  std::vector<Part *> parts() const {
+    std::vector<Part *> p = {mixer_norm_.get(), mixer_.get()};
+    if (ff_) {
+      p.push_back(ff_norm_.get());
+      p.push_back(ff_.get());
+    }
+    return p;
+  }
+  Mixer *mixer_part() override { return mixer_.get(); }
+  std::vector<TensorNeed> own_needs() const {
+    std::vector<TensorNeed> out;
+    // drawn weights: `in` and the columns of `mix` average the copies, so that drawn models keep their scale
+    for (size_t i = 0; i < names_.size(); ++i)
+      out.push_back({names_[i], i % 3 == 2 ? std::vector<int64_t>{streams_, streams_} : std::vector<int64_t>{streams_}, TensorRole::Vector,
+                     streams_ == 1, i % 3 == 1 ? 1.f : 1.f / (float)streams_});
+    return out;
+  }
+  std::vector<TensorNeed> tensor_needs() const override {
+    std::vector<TensorNeed> out;
+    for (Part *p : parts())
+      for (auto &n : p->tensor_needs()) out.push_back(n);
+    for (auto &n : own_needs()) out.push_back(n);
+    return out;
+  }
+  void load(const Loader &l) override {
+    for (Part *p : parts()) p->load(l);
+    joins_.clear();
+    for (auto &n : own_needs()) {
+      if (!n.optional || l.has(n.name)) {
+        joins_.push_back(l.fetch(n));
+        continue;
+      }
+      // one stream whose joining tensors are not stored: in = out = mix = 1, the plain residual sum
+      Weight one;
+      one.dtype = DType::F32;
+      one.rows = one.cols = 1;
+      one.buf.allocate(sizeof(float));
+      const float v = 1.f;
+      LLM_CUDA(cudaMemcpy(one.buf.get(), &v, sizeof(float), cudaMemcpyHostToDevice));
+      joins_.push_back(std::move(one));
+    }
+  }
+  std::vector<std::string> kernel_families() const override {
+    std::vector<std::string> out = {"elementwise"};
+    for (Part *p : parts())
+      for (auto &f : p->kernel_families()) out.push_back(f);
+    return out;
+  }
+  bool capturable() const override {
+    for (Part *p : parts())
+      if (!p->capturable()) return false;
+    return true;
+  }
+  void forward(StepContext &ctx, ResidualStream &stream, LayerCache *cache, StateView *state) override {
+    if (stream.streams != streams_ || stream.hidden != hidden_)
+      LLM_THROW(InvalidArg, "hyper block: built for %d streams of %lld channels, given %d of %lld", streams_, (long long)hidden_,
+                stream.streams, (long long)stream.hidden);
+    ctx.residual_sink = nullptr;            // a result moves every copy: no product can add it as it stores
+    Act h = join(ctx, stream, *mixer_norm_, joins_[0], nullptr, 0);
+    Act r = mixer_->forward(ctx, h, cache, state);
+    leave(stream, r, 1);
+    if (ctx.nothing_read_after) {           // no logits wanted from this step: the stream is read by nobody
+      flush_chain(ctx);
+      stream.pending = Act();
+      return;
+    }
+    if (!ff_) return;
+    const bool few = ctx.rows_read_after && ctx.n_rows_read_after < stream.rows && !stream.picked;
+    h = join(ctx, stream, *ff_norm_, joins_[3], few ? ctx.rows_read_after : nullptr, few ? ctx.n_rows_read_after : 0);
+    r = ff_->forward(ctx, h);
+    leave(stream, r, 4);
+  }
+
+ private:
+  // Applies what is pending, joins the copies with `in`, norms; with `rows` the stream goes on with those rows alone.
+  Act join(StepContext &ctx, ResidualStream &stream, Norm &norm, const Weight &in, const int *rows, int n_rows) {
+    flush_chain(ctx);
+    const int64_t n = rows ? n_rows : stream.rows, H = stream.hidden;
+    float *x_out = stream.resid;
+    int64_t out_stride = stream.stream_stride;
+    if (rows) {
+      x_out = ctx.arena->alloc_n<float>((size_t)streams_ * (size_t)(n * H));
+      out_stride = n * H;
+    }
+    const Act *delta = stream.pending.data ? &stream.pending : nullptr;
+    const int64_t in_stride = stream.spread ? stream.stream_stride : 0;
+    const float *w = nullptr;
+    float eps = 0.f;
+    Act h;
+    if (norm.rms_params(&w, &eps)) {
+      h = ctx.arena->act(ctx.dtype, n, H);
+      kernels::hyper_mix_norm(stream.resid, in_stride, x_out, out_stride, streams_, delta, stream.pending_mix, stream.pending_out,
+                              in.buf.as<float>(), w, eps, h.data, ctx.dtype, rows, (int)n, (int)H, ctx.stream);
+    } else {
+      // any other norm: the joined rows in 32-bit, then the norm's own pass over them
+      float *u = ctx.arena->alloc_n<float>((size_t)(n * H));
+      kernels::hyper_mix_norm(stream.resid, in_stride, x_out, out_stride, streams_, delta, stream.pending_mix, stream.pending_out,
+                              in.buf.as<float>(), nullptr, 0.f, u, DType::F32, rows, (int)n, (int)H, ctx.stream);
+      ResidualStream one;
+      one.resid = u;
+      one.rows = n;
+      one.hidden = H;
+      h = norm.forward(ctx, one);
+    }
+    stream.resid = x_out;
+    stream.stream_stride = out_stride;
+    stream.rows = n;
+    stream.spread = true;
+    stream.pending = Act();
+    stream.pending_mix = stream.pending_out = nullptr;
+    if (rows) stream.picked = true;
+    return h;
+  }
+  void leave(ResidualStream &stream, const Act &r, size_t first) {
+    if (r.dtype != DType::F32 || r.rows != stream.rows || r.cols != stream.hidden || r.ld != stream.hidden)
+      LLM_THROW(Unsupported, "hyper block: a sublayer hands over dense 32-bit rows");
+    stream.pending = r;
+    stream.pending_out = joins_[first].buf.as<float>();
+    stream.pending_mix = joins_[first + 1].buf.as<float>();
+  }
+  int streams_ = 1;
+  int64_t hidden_ = 0;
+  std::unique_ptr<Norm> mixer_norm_, ff_norm_;
+  std::unique_ptr<Mixer> mixer_;
+  std::unique_ptr<FeedForward> ff_;
+  std::vector<std::string> names_;        // in, out, mix of the mixer, then of the feed-forward
+  std::vector<Weight> joins_;
+};
+
 // ---------------------------------------------------------------- parallel block
 // out = x + mixer(h) + ff(h) with h = norm(x): one norm, and both sublayers read its output.  The
 // feed-forward may be absent.  The mixer's result is added to the stream (by its own last product
@@ -913,6 +1097,7 @@ void register_builtin_parts() {
   register_part_raw("mixer", "attention", factory_of<Attention>());
   register_part_raw("feed_forward", "swiglu", factory_of<SwiGLU>());
   register_part_raw("block", "prenorm", factory_of<PreNormBlock>());
+  register_part_raw("block", "hyper", factory_of<HyperBlock>());
 }
 
 }  // namespace llm

@@ -69,6 +69,12 @@ class Mlp : public FeedForward {
 // gate and up rows lie interleaved in one stacked matrix [experts, 2 ff, hidden] and the weight goes on the
 // output.  The result is [parts, T, hidden]: a part per choice, then the
 // shared one's, which the stream adds in that order.
+// Further keys, all optional: `correction`, a vector over the experts that is added to the scores for the CHOICE
+// only (the weights use the scores as they are); `groups` {count, keep, top}: the experts form `count` equal groups
+// of neighbours, a group's score is the sum of its `top` (2) largest corrected scores, and only experts of the `keep`
+// best groups can be chosen; `norm_eps`, added to the sum that `renormalize` divides by; `route_scale`, a factor on
+// the weights; `shared_gate`, a matrix [1, hidden]: the shared feed-forward's result is multiplied by sigmoid(gate x),
+// one number per token (its row rides behind the router's rows in one stacked product).
 class RoutedFeedForward : public FeedForward {
  public:
   RoutedFeedForward(const Json &spec, const BuildEnv &env) : FeedForward(spec, env) {
@@ -96,6 +102,22 @@ class RoutedFeedForward : public FeedForward {
       e.fail("'up', 'down' and 'gate' are patterns with \"{}\" for the expert's number");
     if (!gate_.empty() && !weight_on_output_) e.fail("gated experts take their weight on the output");
     if (r.present("shared")) shared_ = build_as<FeedForward>("feed_forward", r.object("shared"), env);
+    correction_ = r.string_or("correction", "");
+    if (r.present("groups")) {
+      ConfigReader g(r.object("groups"), "moe description: groups");
+      groups_ = (int)g.integer("count");
+      keep_ = (int)g.integer("keep");
+      group_top_ = (int)g.integer_or("top", 2);
+      if (experts_ % groups_) g.fail("'count' must divide the number of experts");
+      if (keep_ > groups_) g.fail("'keep' exceeds 'count'");
+      if ((int64_t)keep_ * (experts_ / groups_) < top_) g.fail("the kept groups hold fewer experts than 'top'");
+    }
+    norm_eps_ = (float)r.number_or("norm_eps", 0.0, false);
+    route_scale_ = (float)r.number_or("route_scale", 1.0, false);
+    shared_gate_ = r.string_or("shared_gate", "");
+    if (!shared_gate_.empty() && !shared_) r.fail("'shared_gate' goes with a 'shared' feed-forward");
+    grouped_route_ = !correction_.empty() || groups_ > 1 || norm_eps_ != 0.f || route_scale_ != 1.f;
+    router_rows_ = shared_gate_.empty() ? experts_ : (experts_ + 1 + 7) / 8 * 8;
   }
   static std::string numbered(const std::string &pattern, int e) {
     std::string s = pattern;
@@ -111,11 +133,25 @@ class RoutedFeedForward : public FeedForward {
     }
     if (shared_)
       for (auto &n : shared_->tensor_needs()) needs.push_back(n);
+    if (!correction_.empty()) needs.push_back({correction_, {(int64_t)experts_}, TensorRole::Vector, false});
+    if (!shared_gate_.empty()) needs.push_back({shared_gate_, {1, hidden_}});
     return needs;
   }
   void load(const Loader &l) override {
     const auto needs = tensor_needs();
-    w_router_ = l.fetch(needs[0]);
+    if (shared_gate_.empty()) {
+      w_router_ = l.fetch(needs[0]);
+    } else {
+      // [router; the shared feed-forward's gate; zeros up to a multiple of 8 rows]
+      const size_t row_bytes = (size_t)hidden_ * dtype_size(l.engine);
+      w_router_.dtype = l.engine;
+      w_router_.rows = router_rows_;
+      w_router_.cols = hidden_;
+      w_router_.buf.allocate((size_t)router_rows_ * row_bytes, true);
+      l.fetch_into(needs[0], l.engine, w_router_.buf.get());
+      l.fetch_into(needs.back(), l.engine, (char *)w_router_.buf.get() + (size_t)experts_ * row_bytes);
+    }
+    if (!correction_.empty()) w_correction_ = l.fetch(needs[needs.size() - (shared_gate_.empty() ? 1 : 2)]);
     const size_t es = dtype_size(l.engine), one = (size_t)(inter_ * hidden_) * es;
     const bool gated = !gate_.empty();
     const size_t per = gated ? 3 : 2, row = (size_t)hidden_ * es;
@@ -152,9 +188,10 @@ class RoutedFeedForward : public FeedForward {
     const int64_t T = x.rows;
     // the shared expert first: its last product may add to the residual stream as it stores
     Act s;
-    if (shared_) s = shared_->forward(ctx, x);
-    const bool s_own = s.data && s.data != (void *)ctx.residual_sink;
     float *const sink = ctx.residual_sink;
+    if (!shared_gate_.empty()) ctx.residual_sink = nullptr;   // a gated result cannot be added by the product that makes it
+    if (shared_) s = shared_->forward(ctx, x);
+    const bool s_own = s.data && s.data != (void *)sink;
     ctx.residual_sink = nullptr;                     // what follows returns its own buffers
     Act z = linear(ctx, x, w_router_, nullptr, DType::F32);
     ctx.residual_sink = sink;
@@ -162,7 +199,11 @@ class RoutedFeedForward : public FeedForward {
     const int n_rows = (int)T * top_;
     int *chosen = ctx.arena->alloc_n<int>((size_t)n_rows);
     float *weight = ctx.arena->alloc_n<float>((size_t)n_rows);
-    kernels::moe_route(z, experts_, top_, score_, renormalize_, chosen, weight, ctx.stream);
+    if (grouped_route_)
+      kernels::moe_route_grouped(z, experts_, top_, score_, correction_.empty() ? nullptr : w_correction_.buf.as<float>(), groups_, keep_,
+                                 group_top_, renormalize_, norm_eps_, route_scale_, chosen, weight, ctx.stream);
+    else
+      kernels::moe_route(z, experts_, top_, score_, renormalize_, chosen, weight, ctx.stream);
     Act out = ctx.arena->act(DType::F32, T, hidden_, top_ + (s_own ? s.parts : 0));
     const bool aligned = x.dtype == DType::BF16 && x.ld % 8 == 0 && (uintptr_t)x.data % 16 == 0;
     if (aligned && fast_switches().moe_tc && kernels::available("moe_tc") && kernels::moe_tc_supported((int)hidden_, (int)inter_)) {
@@ -191,7 +232,11 @@ class RoutedFeedForward : public FeedForward {
     if (s_own) {
       if (s.dtype != DType::F32 || s.rows != T || s.cols != hidden_ || s.ld != hidden_)
         LLM_THROW(Unsupported, "moe: the shared feed-forward must hand over dense 32-bit rows");
-      for (int p = 0; p < s.parts; ++p)
+      for (int p = 0; p < s.parts && !shared_gate_.empty(); ++p)
+        kernels::row_gate((const float *)s.data + (size_t)p * (size_t)s.part_stride,
+                          (float *)out.data + (size_t)(top_ + p) * (size_t)out.part_stride, (const float *)z.data + experts_, z.ld, (int)T,
+                          (int)hidden_, ctx.stream);
+      for (int p = 0; p < s.parts && shared_gate_.empty(); ++p)
         LLM_CUDA(cudaMemcpyAsync((float *)out.data + (size_t)(top_ + p) * (size_t)out.part_stride,
                                  (const float *)s.data + (size_t)p * (size_t)s.part_stride, sizeof(float) * (size_t)(T * hidden_),
                                  cudaMemcpyDeviceToDevice, ctx.stream));
@@ -202,9 +247,11 @@ class RoutedFeedForward : public FeedForward {
  private:
   int64_t hidden_, inter_;
   int experts_, top_, score_, act_;
-  bool renormalize_, weight_on_output_;
-  std::string router_, up_, down_, gate_;
-  Weight w_router_;
+  bool renormalize_, weight_on_output_, grouped_route_ = false;
+  int groups_ = 1, keep_ = 1, group_top_ = 2, router_rows_ = 0;
+  float norm_eps_ = 0.f, route_scale_ = 1.f;
+  std::string router_, up_, down_, gate_, correction_, shared_gate_;
+  Weight w_router_, w_correction_;
   DeviceBuffer w_up_, w_down_;
   std::unique_ptr<FeedForward> shared_;
 };

@@ -9,7 +9,8 @@
 // that width, no value storage).  The products with W_uk and W_uv are moved to the query's side and behind the
 // weighted sum (csrc/latent.cu says how), so a step reads the cached rows once per head and never expands them.
 // A run that the schedule gives another run's cache (ScheduleEntry::cache_from) has no W_dkv of its own: it
-// reads the rows that run appended, with its own W_uk, W_uv and queries.  The rotation is the position part's
+// reads the rows that run appended, with its own W_uk, W_uv and queries.  With `window` w a query at position p sees the
+// rows of positions p - w + 1 .. p only, and the cache gives earlier pages back.  The rotation is the position part's
 // (either pairing; its table carries whatever the scaling puts on cosines and sines); `scale` is the
 // description's.  The reference has no such mixer (its attention: src/libllm/llama.cc:178-225).
 #include <algorithm>
@@ -38,6 +39,7 @@ class LatentAttention : public Mixer {
     q_rank_ = (int)r.integer("q_rank");
     scale_ = (float)r.number_or("scale", 1.0 / std::sqrt((double)(d_ + rot_)), false);
     eps_ = (float)r.number("eps");
+    window_ = (int)r.integer_or("window", 0, 0);
     q_down_ = r.string("q_down");
     q_norm_ = r.string("q_norm");
     q_up_ = r.string("q_up");
@@ -116,7 +118,8 @@ class LatentAttention : public Mixer {
   bool wants_cache() const override { return true; }
   CacheNeed cache_need() const override {
     CacheNeed n;
-    n.kind = "full";
+    n.kind = window_ > 0 ? "window" : "full";    // pages that have left every later query's window go back to the pool
+    n.window = window_;
     n.n_kv_heads = 1;
     n.k_dim = kv_rank_ + rot_;
     n.v_dim = 0;                                       // the values are functions of the key rows
@@ -163,7 +166,8 @@ class LatentAttention : public Mixer {
       flush_chain(ctx);
       Act qb = ctx.arena->act(ctx.dtype, T, (int64_t)n_heads_ * (d_ + rot_));
       kernels::latent_rotate_q(q, qb, n_heads_, d_, rot_, table, table_rows, interleaved, ctx.tok_pos, ctx.stream);
-      kernels::latent_prefill(qb, kv, kr, heads, ctx.seq_start, ctx.n_seqs, ctx.max_q_len, n_heads_, d_, rot_, dv_, scale_, ctx.stream);
+      kernels::latent_prefill(qb, kv, kr, heads, ctx.seq_start, ctx.n_seqs, ctx.max_q_len, n_heads_, d_, rot_, dv_, scale_, ctx.stream,
+                              window_);
       return linear(ctx, heads, w_o_, nullptr, DType::F32, true);
     }
     Act q = linear(ctx, cq, w_uq_, nullptr, DType::F32);
@@ -175,7 +179,7 @@ class LatentAttention : public Mixer {
       // all heads of a token over the cached rows.  A run's partial result is heads x kv_rank 32-bit sums, as many
       // bytes as some tens of cached rows, so a run takes at least 256 keys; within that, enough runs to give
       // every multiprocessor a CTA.  The same for every step of a captured graph.
-      const int max_len = std::max(ctx.max_kv_len, 1);
+      const int max_len = window_ > 0 ? std::min(std::max(ctx.max_kv_len, 1), window_ + 63) : std::max(ctx.max_kv_len, 1);
       const int ctas = std::max(1, T * ((n_heads_ + 31) / 32));
       const int want = std::max(1, (ctx.sm_count + ctas - 1) / ctas);
       const int most = std::max(1, max_len / 256);
@@ -183,10 +187,10 @@ class LatentAttention : public Mixer {
       float *ws = nullptr;
       if (n_splits > 1) ws = ctx.arena->alloc_n<float>(kernels::latent_decode_floats(T, n_heads_, kv_rank_, n_splits));
       kernels::latent_decode(qa, cache->k, cache->page_size, ctx.tok_seq, ctx.tok_pos, cache->page_table, cache->table_width, n_heads_,
-                             kv_rank_, rot_, n_splits, scale_, mixed, ws, ctx.stream);
+                             kv_rank_, rot_, n_splits, scale_, mixed, ws, ctx.stream, window_);
     } else {
       kernels::attention_generic(qa, mixed, cache->k, cache->k, ctx.tok_seq, ctx.tok_pos, cache->page_table, cache->table_width, n_heads_,
-                                 1, row, kv_rank_, cache->page_size, 0, 0, scale_, nullptr, 0, ctx.stream, 0, row);
+                                 1, row, kv_rank_, cache->page_size, window_, 0, scale_, nullptr, 0, ctx.stream, 0, row);
     }
     kernels::latent_expand(mixed, w_uv_.buf.get(), heads, n_heads_, kv_rank_, dv_, ctx.stream);
     return linear(ctx, heads, w_o_, nullptr, DType::F32, true);
@@ -194,7 +198,7 @@ class LatentAttention : public Mixer {
 
  private:
   int64_t hidden_, down_rows_;
-  int n_heads_, d_, rot_, dv_, kv_rank_, q_rank_;
+  int n_heads_, d_, rot_, dv_, kv_rank_, q_rank_, window_ = 0;
   float scale_, eps_;
   std::string q_down_, q_norm_, q_up_, kv_down_, kv_norm_, k_up_, v_up_, o_;
   std::unique_ptr<PositionEncoding> position_;

@@ -172,11 +172,20 @@ class Arena {
 
 // The 32-bit residual stream and an addition that has not been applied yet.  The addition is
 // folded into the next norm's pass over the row.
+//
+// A model may carry `streams` copies of the stream (ModelSpec::streams; a block of kind "hyper" joins its sublayers to
+// them): copy s lies stream_stride floats behind copy s - 1.  While `spread` is false only copy 0 has been written and
+// the others are equal to it.  A pending result then moves all copies at once, x_t <- sum_s pending_mix[s, t] x_s +
+// pending_out[t] y (device pointers: a matrix [streams, streams] indexed [from, to] and a vector [streams]).
 struct ResidualStream {
   float *resid = nullptr;
   int64_t rows = 0, hidden = 0;
   Act pending;                       // data == nullptr: nothing pending
   bool picked = false;               // the rows are StepContext::rows_read_after, in that order, and no others
+  int streams = 1;
+  int64_t stream_stride = 0;
+  bool spread = true;
+  const float *pending_mix = nullptr, *pending_out = nullptr;
 };
 
 // What load() fetches tensors through: the files of a model folder, tensors in host memory, or
@@ -236,6 +245,12 @@ class Norm : public Part {
   // Applies stream.pending (in 32-bit) first.  With `rows` only those rows are normalised and the
   // residual stream is left as it is.
   virtual Act forward(StepContext &ctx, ResidualStream &stream, const int *rows = nullptr, int n_rows = 0) = 0;
+  // An RMS norm hands over its weight as it is applied (32-bit, device) and its eps, so that a block with a pass of its own
+  // over the rows can run the norm inside it; any other norm says false and is run through forward().
+  virtual bool rms_params(const float **weight, float *eps) const {
+    (void)weight, (void)eps;
+    return false;
+  }
 };
 
 // What an attention-like mixer tells its position part about the stacked q|k|v rows.
@@ -289,6 +304,8 @@ class Block : public Part {
  public:
   using Part::Part;
   virtual Mixer *mixer_part() = 0;
+  // Copies of the residual stream this block works on (ResidualStream::streams); a model's blocks all say the same.
+  virtual int streams() const { return 1; }
   // Fixed-size state per sequence of one run of the block: the mixer's, and what the block keeps itself.
   virtual std::vector<StateNeed> state_need() {
     Mixer *m = mixer_part();

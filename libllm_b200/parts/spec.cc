@@ -31,6 +31,7 @@ Json ModelSpec::to_json() const {
   j.set("logit_scale", logit_scale);
   j.set("logit_softcap", logit_softcap);
   j.set("ignore_tensors", Json::list(ignore_tensors));
+  j.set("streams", (int64_t)streams);
   return j;
 }
 
@@ -81,6 +82,7 @@ ModelSpec ModelSpec::from_json(const Json &j) {
   s.embedding_scale = r.number_or("embedding_scale", 1.0);
   s.logit_scale = r.number_or("logit_scale", 1.0);
   s.logit_softcap = r.number_or("logit_softcap", 0.0, false);
+  s.streams = (int)r.integer_or("streams", 1);
   const Json &ig = j.get("ignore_tensors");
   if (ig.is_array())
     for (const auto &t : ig.items())

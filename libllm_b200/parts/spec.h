@@ -22,6 +22,7 @@
 //   feed_forward "moe":    hidden, experts, top, score, renormalize, weight_on, router, expert {..}, shared
 //   block "prenorm":       mixer_norm, mixer, ff_norm, ff (descriptions; ff and ff_norm may be null), mixer_conv {taps, weight, hidden}
 //   block "parallel":      norm, mixer, ff (a description or null): x + mixer(norm x) + ff(norm x)
+//   block "hyper":         the pre-norm block over several copies of the residual stream (parts/builtin.cc)
 #pragma once
 #include <string>
 #include <vector>
@@ -57,6 +58,9 @@ struct ModelSpec {
   double embedding_scale = 1.0;           // token rows are multiplied by this before the first layer
   double logit_scale = 1.0;               // logits are multiplied by this ...
   double logit_softcap = 0.0;             // ... and, if positive, bounded: cap * tanh(logit / cap)
+  // Copies of the residual stream the model carries (blocks of kind "hyper").  All start as the token's row; the last
+  // norm reads their sum.
+  int streams = 1;
   // Tensors that may lie in the files without any part asking for them ('*' matches any run of
   // characters).  Other unexpected tensors are reported as a warning, not an error.
   std::vector<std::string> ignore_tensors;

@@ -30,6 +30,7 @@ struct TensorNeed {
   std::vector<int64_t> shape;
   TensorRole role = TensorRole::Matrix;
   bool optional = false;
+  float drawn_scale = 1.f;           // where tensors are drawn instead of read: the drawn values times this
 };
 
 struct WrongShape {
