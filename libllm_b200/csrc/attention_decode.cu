@@ -40,7 +40,7 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
                         int n_kv, int page_size, int chunk, int window, int block, int sink, float scale_log2,
                         float *__restrict__ ws_o, float *__restrict__ ws_ml, int n_splits,
                         __nv_bfloat16 *__restrict__ out, long long out_stride, const float *__restrict__ gate,
-                        long long gate_stride, int gate_per_channel) {
+                        long long gate_stride, int gate_per_channel, float null_log2) {
   constexpr int LPK = D / 8;                 // lanes per key
   constexpr int GPW = 32 / LPK;              // lane groups per warp
   constexpr int GROUPS = (AD_THREADS / 32) * GPW;
@@ -220,7 +220,7 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
     const int head = kvh * G + h;
     if (n_splits == 1) {
       const float gf = gate ? 1.f / (1.f + expf(-gate[(size_t)b * gate_stride + (gate_per_channel ? head * D + c : head)])) : 1.f;
-      out[(size_t)b * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(O / L * gf);
+      out[(size_t)b * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(O * softmax_norm_factor(M, L, null_log2) * gf);
     } else {
       const size_t slot = ((size_t)b * n_heads + head) * n_splits + split;
       ws_o[slot * D + c] = O;
@@ -237,7 +237,7 @@ __global__ void attention_decode_combine_kernel(const float *__restrict__ ws_o, 
                                                 const int *__restrict__ tok_pos, int n_heads, int D, int chunk,
                                                 int window, int block, int sink, int n_splits, __nv_bfloat16 *__restrict__ out,
                                                 long long out_stride, const float *__restrict__ gate,
-                                                long long gate_stride, int gate_per_channel) {
+                                                long long gate_stride, int gate_per_channel, float null_log2) {
   grid_dependents_launch();
   grid_dependency_wait();
   const int head = blockIdx.x, b = blockIdx.y;
@@ -256,6 +256,7 @@ __global__ void attention_decode_combine_kernel(const float *__restrict__ ws_o, 
   float L = 0.f;
   for (int s = 0; s <= last; ++s)
     if (live(s)) L += ws_ml[(slot0 + s) * 2 + 1] * exp2f(ws_ml[(slot0 + s) * 2] - M);
+  const float norm = softmax_norm_factor(M, L, null_log2);     // the key without a value joins the sum here, once
   // a gate per (sequence, head), or per channel of the head: the result is multiplied by its sigmoid
   const float head_gf = gate && !gate_per_channel ? 1.f / (1.f + expf(-gate[(size_t)b * gate_stride + head])) : 1.f;
   for (int c = threadIdx.x; c < D; c += blockDim.x) {
@@ -263,7 +264,7 @@ __global__ void attention_decode_combine_kernel(const float *__restrict__ ws_o, 
     float O = 0.f;
     for (int s = 0; s <= last; ++s)
       if (live(s)) O += ws_o[(slot0 + s) * D + c] * exp2f(ws_ml[(slot0 + s) * 2] - M);
-    out[(size_t)b * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(O / L * gf);
+    out[(size_t)b * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(O * norm * gf);
   }
 }
 
@@ -271,20 +272,21 @@ template <int D, int G>
 static int launch_decode(const void *q, long long q_stride, const void *kc, const void *vc, const int *tok_pos,
                          const int *page_table, int pt_stride, int n_seqs, int n_kv, int page_size, int chunk,
                          int n_splits, int window, int block, int sink, float scale, float *ws_o, float *ws_ml, void *out,
-                         long long out_stride, const float *gate, long long gate_stride, int gate_per_channel, cudaStream_t stream) {
+                         long long out_stride, const float *gate, long long gate_stride, int gate_per_channel, float null_score,
+                         cudaStream_t stream) {
   dim3 grid(n_splits, n_kv, n_seqs);
   const size_t smem = (size_t)((chunk + page_size - 1) / page_size) * sizeof(int);
   LLM_REQUIRE(smem <= 16 * 1024, "attention_decode: a chunk of %d keys spans too many pages", chunk);
   llm_launch(attention_decode_kernel<D, G>, grid, dim3(AD_THREADS), smem, stream,
       (const __nv_bfloat16 *)q, q_stride, (const __nv_bfloat16 *)kc, (const __nv_bfloat16 *)vc, tok_pos, page_table,
       pt_stride, n_kv, page_size, chunk, window, block, sink, scale * 1.4426950408889634f, ws_o, ws_ml, n_splits,
-      (__nv_bfloat16 *)out, out_stride, gate, gate_stride, gate_per_channel);
+      (__nv_bfloat16 *)out, out_stride, gate, gate_stride, gate_per_channel, null_score * 1.4426950408889634f);
   LLM_CHECK_LAUNCH("attention_decode");
   if (n_splits > 1) {
     dim3 cgrid(n_kv * G, n_seqs);
     llm_launch(attention_decode_combine_kernel, cgrid, dim3(D < 64 ? 32 : 64), 0, stream, (const float *)ws_o,
                (const float *)ws_ml, tok_pos, n_kv * G, D, chunk, window, block, sink, n_splits, (__nv_bfloat16 *)out, out_stride,
-               gate, gate_stride, gate_per_channel);
+               gate, gate_stride, gate_per_channel, null_score * 1.4426950408889634f);
     LLM_CHECK_LAUNCH("attention_decode_combine");
   }
   return LLM_OK;
@@ -303,12 +305,13 @@ LLM_EXPORT int llm_attention_decode_supports(int d, int group) {
 // `gate` (32-bit, one value per sequence and head, row stride gate_stride; null: none): a head's result is
 // multiplied by sigmoid(gate); with gate_per_channel the gate has a value per channel of the concatenated heads.
 // `sink` > 0 with a window: the first `sink` positions stay visible beyond the window.
-LLM_EXPORT int llm_attention_decode_sink(const void *q, long long q_stride, void *out, long long out_stride,
+// `null_score`: every query also sees one key of that score that has no value (minus infinity: none).
+LLM_EXPORT int llm_attention_decode_null(const void *q, long long q_stride, void *out, long long out_stride,
                                          const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                                          int pt_stride, int n_seqs, int n_heads, int n_kv, int d, int page_size,
                                          int chunk, int n_splits, int window, int block, int sink, float scale, float *ws_o,
                                          float *ws_ml, const float *gate, long long gate_stride, int gate_per_channel,
-                                         cudaStream_t stream) {
+                                         float null_score, cudaStream_t stream) {
   if (n_seqs == 0) return LLM_OK;
   LLM_REQUIRE(sink >= 0 && (sink == 0 || (window > 0 && block == 0)), "attention_decode: kept first positions go with a window");
   LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_kv > 0 && n_kv <= 65535 && n_heads % n_kv == 0, "attention_decode: bad sizes");
@@ -321,12 +324,23 @@ LLM_EXPORT int llm_attention_decode_sink(const void *q, long long q_stride, void
   if (d == DD && group == GG)                                                                                   \
     return launch_decode<DD, GG>(q, q_stride, kc, vc, tok_pos, page_table, pt_stride, n_seqs, n_kv, page_size, \
                                  chunk, n_splits, window, block, sink, scale, ws_o, ws_ml, out, out_stride, gate, gate_stride, \
-                                 gate_per_channel, stream);
+                                 gate_per_channel, null_score, stream);
 #define AD_CASES(DD) AD_CASE(DD, 1) AD_CASE(DD, 2) AD_CASE(DD, 3) AD_CASE(DD, 4) AD_CASE(DD, 8)
   AD_CASES(16) AD_CASES(32) AD_CASES(64) AD_CASES(128)
 #undef AD_CASES
 #undef AD_CASE
   LLM_FAIL("attention_decode: no kernel for head size %d, group %d", d, group);
+}
+
+LLM_EXPORT int llm_attention_decode_sink(const void *q, long long q_stride, void *out, long long out_stride,
+                                         const void *kc, const void *vc, const int *tok_pos, const int *page_table,
+                                         int pt_stride, int n_seqs, int n_heads, int n_kv, int d, int page_size,
+                                         int chunk, int n_splits, int window, int block, int sink, float scale, float *ws_o,
+                                         float *ws_ml, const float *gate, long long gate_stride, int gate_per_channel,
+                                         cudaStream_t stream) {
+  return llm_attention_decode_null(q, q_stride, out, out_stride, kc, vc, tok_pos, page_table, pt_stride, n_seqs, n_heads, n_kv, d,
+                                   page_size, chunk, n_splits, window, block, sink, scale, ws_o, ws_ml, gate, gate_stride,
+                                   gate_per_channel, -INFINITY, stream);
 }
 
 LLM_EXPORT int llm_attention_decode_gated(const void *q, long long q_stride, void *out, long long out_stride,

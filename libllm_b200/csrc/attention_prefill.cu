@@ -37,7 +37,7 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
                          long long out_stride, const __nv_bfloat16 *__restrict__ kc,
                          const __nv_bfloat16 *__restrict__ vc, const int *__restrict__ seq_start,
                          const int *__restrict__ seq_past, const int *__restrict__ page_table, int pt_stride,
-                         int n_heads, int n_kv, int window, int block, int sink, float scale_log2) {
+                         int n_heads, int n_kv, int window, int block, int sink, float scale_log2, float null_log2) {
   constexpr int LD = D + 8;                                  // padded row, in elements
   constexpr int CHUNKS = D / 8;                              // 16-byte pieces of a row
   constexpr int KS = D / 16;                                 // k-steps of Q K^T
@@ -215,7 +215,8 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
   }
   const int row_a = warp * 16 + g, row_b = row_a + 8;
-  const float inv_a = 1.f / l_run[0], inv_b = 1.f / l_run[1];
+  const float inv_a = softmax_norm_factor(m_run[0] == -INFINITY ? -INFINITY : m_run[0] * scale_log2, l_run[0], null_log2);
+  const float inv_b = softmax_norm_factor(m_run[1] == -INFINITY ? -INFINITY : m_run[1] * scale_log2, l_run[1], null_log2);
   __nv_bfloat16 *oa = out + (size_t)(q0 + r0 + row_a) * out_stride + (size_t)h * D + 2 * t;
   __nv_bfloat16 *ob = out + (size_t)(q0 + r0 + row_b) * out_stride + (size_t)h * D + 2 * t;
 #pragma unroll
@@ -229,7 +230,7 @@ template <int D>
 static int launch_prefill(const void *q, long long q_stride, void *out, long long out_stride, const void *kc,
                           const void *vc, const int *seq_start, const int *seq_past, const int *page_table,
                           int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int window, int block, int sink, float scale,
-                          cudaStream_t stream) {
+                          float null_score, cudaStream_t stream) {
   constexpr int LD = D + 8;
   const size_t smem = (size_t)(AP_BM + 4 * AP_BN) * LD * sizeof(__nv_bfloat16);
   auto kern = attention_prefill_kernel<D>;
@@ -237,7 +238,7 @@ static int launch_prefill(const void *q, long long q_stride, void *out, long lon
   dim3 grid((max_q_len + AP_BM - 1) / AP_BM, n_heads, n_seqs);
   llm_launch(kern, grid, dim3(AP_WARPS * 32), smem, stream, (const __nv_bfloat16 *)q, q_stride, (__nv_bfloat16 *)out,
              out_stride, (const __nv_bfloat16 *)kc, (const __nv_bfloat16 *)vc, seq_start, seq_past, page_table,
-             pt_stride, n_heads, n_kv, window, block, sink, scale * 1.4426950408889634f);
+             pt_stride, n_heads, n_kv, window, block, sink, scale * 1.4426950408889634f, null_score * 1.4426950408889634f);
   LLM_CHECK_LAUNCH("attention_prefill");
   return LLM_OK;
 }
@@ -251,11 +252,12 @@ LLM_EXPORT int llm_attention_prefill_supports(int d, int page_size) {
 // [pages, kv_heads, 64, d]; sequence b owns rows seq_start[b]..seq_start[b+1]-1, which
 // stand at positions seq_past[b].. of the sequence; max_q_len bounds the rows of a sequence.
 // `sink` > 0 with a window: the first `sink` positions of a sequence stay visible to all its later queries.
-LLM_EXPORT int llm_attention_prefill(const void *q, long long q_stride, void *out, long long out_stride,
-                                     const void *kc, const void *vc, const int *seq_start, const int *seq_past,
-                                     const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads,
-                                     int n_kv, int d, int page_size, int window, int block, int sink, float scale,
-                                     cudaStream_t stream) {
+// `null_score`: every query also sees one key of that score that has no value (minus infinity: none).
+LLM_EXPORT int llm_attention_prefill_null(const void *q, long long q_stride, void *out, long long out_stride,
+                                          const void *kc, const void *vc, const int *seq_start, const int *seq_past,
+                                          const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads,
+                                          int n_kv, int d, int page_size, int window, int block, int sink, float scale,
+                                          float null_score, cudaStream_t stream) {
   if (n_seqs == 0 || max_q_len == 0) return LLM_OK;
   LLM_REQUIRE(sink >= 0 && (sink == 0 || (window > 0 && block == 0)), "attention_prefill: kept first positions go with a window");
   LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_heads > 0 && n_heads <= 65535 && n_kv > 0 && n_heads % n_kv == 0,
@@ -270,8 +272,17 @@ LLM_EXPORT int llm_attention_prefill(const void *q, long long q_stride, void *ou
 #define AP_CASE(DD)                                                                                                  \
   if (d == DD)                                                                                                       \
     return launch_prefill<DD>(q, q_stride, out, out_stride, kc, vc, seq_start, seq_past, page_table, pt_stride,      \
-                              n_seqs, max_q_len, n_heads, n_kv, window, block, sink, scale, stream);
+                              n_seqs, max_q_len, n_heads, n_kv, window, block, sink, scale, null_score, stream);
   AP_CASE(16) AP_CASE(32) AP_CASE(48) AP_CASE(64) AP_CASE(80) AP_CASE(96) AP_CASE(112) AP_CASE(128)
 #undef AP_CASE
   LLM_FAIL("attention_prefill: no kernel for head size %d", d);
+}
+
+LLM_EXPORT int llm_attention_prefill(const void *q, long long q_stride, void *out, long long out_stride,
+                                     const void *kc, const void *vc, const int *seq_start, const int *seq_past,
+                                     const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads,
+                                     int n_kv, int d, int page_size, int window, int block, int sink, float scale,
+                                     cudaStream_t stream) {
+  return llm_attention_prefill_null(q, q_stride, out, out_stride, kc, vc, seq_start, seq_past, page_table, pt_stride, n_seqs, max_q_len,
+                                    n_heads, n_kv, d, page_size, window, block, sink, scale, -INFINITY, stream);
 }

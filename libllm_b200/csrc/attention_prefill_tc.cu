@@ -86,7 +86,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16 *__restrict__ out,
                             long long out_stride, const int *__restrict__ seq_start, const int *__restrict__ seq_past,
                             const int *__restrict__ page_table, int pt_stride, int n_heads, int n_kv, int window, int block,
-                            int sink, float scale_log2, int *status) {
+                            int sink, float scale_log2, float null_log2, int *status) {
   using S = FtShape<D>;
   constexpr int STAGES = S::STAGES;
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -378,7 +378,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const float l_row = xch[row] + xch[FT_BM + row];
     if (ok) {
       tc_fence_after();
-      const float inv = 1.f / l_row;
+      const float inv = softmax_norm_factor(ref, l_row, null_log2);
       __nv_bfloat16 *dst = out + (size_t)(q0 + r0 + row) * out_stride + (size_t)h * D + half * HD;
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -464,7 +464,7 @@ attention_prefill_wide_kernel(const __grid_constant__ CUtensorMap map_q, const _
                               const __grid_constant__ CUtensorMap map_v, __nv_bfloat16 *__restrict__ out,
                               long long out_stride, const int *__restrict__ seq_start, const int *__restrict__ seq_past,
                               const int *__restrict__ page_table, int pt_stride, int n_heads, int n_kv, int window, int block,
-                              float scale_log2, int *status) {
+                              float scale_log2, float null_log2, int *status) {
   using S = FwShape<D>;
   constexpr int STAGES = S::STAGES;
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -780,7 +780,7 @@ attention_prefill_wide_kernel(const __grid_constant__ CUtensorMap map_q, const _
     if (ok && j_hi > j_lo) ok = __all_sync(0xffffffffu, mbar_wait(bar_ofull + 8 * x, (j_hi - j_lo - 1) & 1, abort_flag, status, 38));
     if (ok && j_hi > j_lo) {
       tc_fence_after();
-      const float inv = 1.f / l_run;
+      const float inv = softmax_norm_factor(ref, l_run, null_log2);
       __nv_bfloat16 *dst = out + (size_t)(q0 + r0 + x * 128 + row) * out_stride + (size_t)h * D;
 #pragma unroll
       for (int c0 = 0; c0 < D; c0 += 32) {
@@ -826,7 +826,7 @@ template <int D>
 int launch_prefill_tc(const void *q, long long q_stride, long long n_tokens, void *out, long long out_stride,
                       const void *kc, const void *vc, long long n_pages, const int *seq_start, const int *seq_past,
                       const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int window,
-                      int block, int sink, float scale, int form, int *status, cudaStream_t stream) {
+                      int block, int sink, float scale, float null_score, int form, int *status, cudaStream_t stream) {
   using S = FtShape<D>;
   if (sink > 0) form = 1;                 // kept first positions: the form of 128 rows walks their tiles
   CUtensorMap map_q, map_k, map_v;
@@ -847,7 +847,7 @@ int launch_prefill_tc(const void *q, long long q_stride, long long n_tokens, voi
     dim3 grid(n_heads, n_seqs, (max_q_len + FW_BM - 1) / FW_BM);
     LLM_CHECK_CUDA(llm_launch(kern, grid, dim3(FW_THREADS), W::SMEM, stream, map_q, map_k, map_v, (__nv_bfloat16 *)out,
                               out_stride, seq_start, seq_past, page_table, pt_stride, n_heads, n_kv, window, block,
-                              scale * 1.4426950408889634f, status),
+                              scale * 1.4426950408889634f, null_score * 1.4426950408889634f, status),
                    "attention_prefill_tc launch");
     return LLM_OK;
   }
@@ -856,7 +856,7 @@ int launch_prefill_tc(const void *q, long long q_stride, long long n_tokens, voi
   dim3 grid(n_heads, n_seqs, (max_q_len + FT_BM - 1) / FT_BM);
   LLM_CHECK_CUDA(llm_launch(kern, grid, dim3(FT_THREADS), S::SMEM, stream, map_q, map_k, map_v, (__nv_bfloat16 *)out,
                             out_stride, seq_start, seq_past, page_table, pt_stride, n_heads, n_kv, window, block, sink,
-                            scale * 1.4426950408889634f, status),
+                            scale * 1.4426950408889634f, null_score * 1.4426950408889634f, status),
                  "attention_prefill_tc launch");
   return LLM_OK;
 }
@@ -874,12 +874,13 @@ LLM_EXPORT int llm_attention_prefill_tc_supports(int d, int page_size) {
 // int, may be null) receives a non-zero code if a wait inside the kernel ran out of time.  `form`: 0 the
 // library chooses (the wide form when a sequence brings more than 128 rows), 1 CTAs of 128 rows, 2 of 256.
 // `sink` > 0 with a window: the first `sink` positions of a sequence stay visible to all its later queries (form 1).
-LLM_EXPORT int llm_attention_prefill_tc(const void *q, long long q_stride, long long n_tokens, void *out,
-                                        long long out_stride, const void *kc, const void *vc, long long n_pages,
-                                        const int *seq_start, const int *seq_past, const int *page_table,
-                                        int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int d,
-                                        int page_size, int window, int block, int sink, float scale, int form, int *status,
-                                        cudaStream_t stream) {
+// `null_score`: every query also sees one key of that score that has no value (minus infinity: none).
+LLM_EXPORT int llm_attention_prefill_tc_null(const void *q, long long q_stride, long long n_tokens, void *out,
+                                             long long out_stride, const void *kc, const void *vc, long long n_pages,
+                                             const int *seq_start, const int *seq_past, const int *page_table,
+                                             int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int d,
+                                             int page_size, int window, int block, int sink, float scale, float null_score,
+                                             int form, int *status, cudaStream_t stream) {
   if (n_seqs == 0 || max_q_len == 0) return LLM_OK;
   LLM_REQUIRE(sink >= 0 && (sink == 0 || (window > 0 && block == 0)), "attention_prefill_tc: kept first positions go with a window");
   LLM_REQUIRE(form >= 0 && form <= 2, "attention_prefill_tc: form %d is not one of 0, 1, 2", form);
@@ -895,7 +896,18 @@ LLM_EXPORT int llm_attention_prefill_tc(const void *q, long long q_stride, long 
   LLM_REQUIRE(n_pages * n_kv * FT_BN < (1ll << 31), "attention_prefill_tc: the cache has too many rows for one tensor map");
   if (d == 64)
     return launch_prefill_tc<64>(q, q_stride, n_tokens, out, out_stride, kc, vc, n_pages, seq_start, seq_past, page_table,
-                                 pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, block, sink, scale, form, status, stream);
+                                 pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, block, sink, scale, null_score, form, status, stream);
   return launch_prefill_tc<128>(q, q_stride, n_tokens, out, out_stride, kc, vc, n_pages, seq_start, seq_past, page_table,
-                                pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, block, sink, scale, form, status, stream);
+                                pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, block, sink, scale, null_score, form, status, stream);
+}
+
+LLM_EXPORT int llm_attention_prefill_tc(const void *q, long long q_stride, long long n_tokens, void *out,
+                                        long long out_stride, const void *kc, const void *vc, long long n_pages,
+                                        const int *seq_start, const int *seq_past, const int *page_table,
+                                        int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int d,
+                                        int page_size, int window, int block, int sink, float scale, int form, int *status,
+                                        cudaStream_t stream) {
+  return llm_attention_prefill_tc_null(q, q_stride, n_tokens, out, out_stride, kc, vc, n_pages, seq_start, seq_past, page_table,
+                                       pt_stride, n_seqs, max_q_len, n_heads, n_kv, d, page_size, window, block, sink, scale,
+                                       -INFINITY, form, status, stream);
 }

@@ -178,6 +178,17 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// The factor a softmax's weighted sum is multiplied by at the end, when every query also sees one key of score
+// `null_log2` that has no value: sums o and l were taken relative to `ref` (both in the exponent's base-2 units), and the
+// result is o / (l + 2^(null_log2 - ref)), computed against the larger of the two references so that nothing overflows.
+// null_log2 minus infinity: no such key, 1 / l.
+__device__ __forceinline__ float softmax_norm_factor(float ref, float l, float null_log2) {
+  if (!(null_log2 > -INFINITY)) return 1.f / l;
+  const float top = fmaxf(ref, null_log2);
+  const float a = ref == -INFINITY ? 0.f : exp2f(ref - top);
+  return a / (l * a + exp2f(null_log2 - top));
+}
+
 // Sum over a block with a fixed order of additions: warps first, then the warp totals
 // in warp order.  The result does not depend on how many rows the launch has.
 template <int THREADS>

@@ -355,21 +355,21 @@ void rope_pairs_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, i
 LLM_KERNEL("attention_generic", llm_attention_generic_ld, int, const void *, long long, void *, long long, const void *, const void *,
            const int *, const int *, const int *, int, int, int, int, int, int, int, int, int, int, int, float, const float *, long long,
            float, cudaStream_t)
-LLM_KERNEL("attention_decode", llm_attention_decode_sink, const void *, long long, void *, long long, const void *, const void *,
+LLM_KERNEL("attention_decode", llm_attention_decode_null, const void *, long long, void *, long long, const void *, const void *,
            const int *, const int *, int, int, int, int, int, int, int, int, int, int, int, float, float *, float *, const float *,
-           long long, int, cudaStream_t)
+           long long, int, float, cudaStream_t)
 LLM_KERNEL("attention_decode_tc", llm_attention_decode_tc, const float *, long long, int, long long, const float *, int, int,
            const int *, const int *, int, void *, void *, int, int, int, int, int, int, int, int, int, int, int, float, float *,
            float *, int *, void *, long long, cudaStream_t)
-LLM_KERNEL("attention_prefill", llm_attention_prefill, const void *, long long, void *, long long, const void *, const void *,
-           const int *, const int *, const int *, int, int, int, int, int, int, int, int, int, int, float, cudaStream_t)
+LLM_KERNEL("attention_prefill", llm_attention_prefill_null, const void *, long long, void *, long long, const void *, const void *,
+           const int *, const int *, const int *, int, int, int, int, int, int, int, int, int, int, float, float, cudaStream_t)
 LLM_KERNEL("elementwise", llm_head_gate, void *, int, long long, const float *, long long, int, int, int, cudaStream_t)
 void head_gate(const Act &out, const float *gate, long long gate_stride, int n_heads, int dv, cudaStream_t s) {
   LLM_CALL("elementwise", llm_head_gate, out.data, code(out.dtype), (long long)out.ld, gate, gate_stride, (int)out.rows, n_heads, dv, s);
 }
-LLM_KERNEL("attention_prefill_tc", llm_attention_prefill_tc, const void *, long long, long long, void *, long long, const void *,
-           const void *, long long, const int *, const int *, const int *, int, int, int, int, int, int, int, int, int, int, float, int,
-           int *, cudaStream_t)
+LLM_KERNEL("attention_prefill_tc", llm_attention_prefill_tc_null, const void *, long long, long long, void *, long long, const void *,
+           const void *, long long, const int *, const int *, const int *, int, int, int, int, int, int, int, int, int, int, float, float,
+           int, int *, cudaStream_t)
 
 void attention_generic(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_seq, const int *tok_pos,
                        const int *page_table, int pt_stride, int n_heads, int n_kv, int d, int dv, int page_size, int window,
@@ -458,11 +458,11 @@ bool attention_decode_supported(int d, int group) {
 void attention_decode(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                       int pt_stride, int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window,
                       int block, float scale, float *ws_o, float *ws_ml, const float *gate, long long gate_stride,
-                      cudaStream_t s, int sink, bool gate_per_channel) {
+                      cudaStream_t s, int sink, bool gate_per_channel, float null_score) {
   const int B = (int)q.rows;
-  LLM_CALL("attention_decode", llm_attention_decode_sink, q.data, (long long)(B > 1 ? q.ld : q.cols), out.data,
+  LLM_CALL("attention_decode", llm_attention_decode_null, q.data, (long long)(B > 1 ? q.ld : q.cols), out.data,
            (long long)(B > 1 ? out.ld : out.cols), kc, vc, tok_pos, page_table, pt_stride, B, n_heads, n_kv, d, page_size, chunk,
-           n_splits, window, block, sink, scale, ws_o, ws_ml, gate, gate_stride, gate_per_channel ? 1 : 0, s);
+           n_splits, window, block, sink, scale, ws_o, ws_ml, gate, gate_stride, gate_per_channel ? 1 : 0, null_score, s);
 }
 bool attention_decode_tc_supported(int d, int page_size, int group) {
   static auto f = resolve<int (*)(int, int, int)>("attention_decode_tc", "llm_attention_decode_tc_supports");
@@ -487,9 +487,9 @@ bool attention_prefill_supported(int d, int page_size) {
 }
 void attention_prefill(const Act &q, const Act &out, const void *kc, const void *vc, const int *seq_start, const int *seq_past,
                        const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int d,
-                       int page_size, int window, int block, float scale, cudaStream_t s, int sink) {
-  LLM_CALL("attention_prefill", llm_attention_prefill, q.data, (long long)q.ld, out.data, (long long)out.ld, kc, vc, seq_start,
-           seq_past, page_table, pt_stride, n_seqs, max_q_len, n_heads, n_kv, d, page_size, window, block, sink, scale, s);
+                       int page_size, int window, int block, float scale, cudaStream_t s, int sink, float null_score) {
+  LLM_CALL("attention_prefill", llm_attention_prefill_null, q.data, (long long)q.ld, out.data, (long long)out.ld, kc, vc, seq_start,
+           seq_past, page_table, pt_stride, n_seqs, max_q_len, n_heads, n_kv, d, page_size, window, block, sink, scale, null_score, s);
 }
 bool attention_prefill_tc_supported(int d, int page_size) {
   static auto f = resolve<int (*)(int, int)>("attention_prefill_tc", "llm_attention_prefill_tc_supports");
@@ -498,10 +498,10 @@ bool attention_prefill_tc_supported(int d, int page_size) {
 void attention_prefill_tc(const Act &q, const Act &out, const void *kc, const void *vc, long long n_pages, const int *seq_start,
                           const int *seq_past, const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads,
                           int n_kv, int d, int page_size, int window, int block, float scale, int *status, cudaStream_t s,
-                          int sink) {
-  LLM_CALL("attention_prefill_tc", llm_attention_prefill_tc, q.data, (long long)q.ld, (long long)q.rows, out.data,
+                          int sink, float null_score) {
+  LLM_CALL("attention_prefill_tc", llm_attention_prefill_tc_null, q.data, (long long)q.ld, (long long)q.rows, out.data,
            (long long)out.ld, kc, vc, n_pages, seq_start, seq_past, page_table, pt_stride, n_seqs, max_q_len, n_heads, n_kv, d,
-           page_size, window, block, sink, scale, 0, status, s);
+           page_size, window, block, sink, scale, null_score, 0, status, s);
 }
 
 // ---------------------------------------------------------------- routed feed-forward

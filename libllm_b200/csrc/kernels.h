@@ -160,7 +160,7 @@ bool attention_decode_supported(int d, int group);
 void attention_decode(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                       int pt_stride, int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window,
                       int block, float scale, float *ws_o, float *ws_ml, const float *gate, long long gate_stride,
-                      cudaStream_t s, int sink = 0, bool gate_per_channel = false);
+                      cudaStream_t s, int sink = 0, bool gate_per_channel = false, float null_score = NO_NULL_KEY);
 bool attention_decode_tc_supported(int d, int page_size, int group);
 int attention_decode_tc_ctas_per_sm(int d);
 void attention_decode_tc(const Act &qkv, const float *table, int table_rows, int rot_dim, const int *tok_pos,
@@ -170,12 +170,12 @@ void attention_decode_tc(const Act &qkv, const float *table, int table_rows, int
 bool attention_prefill_supported(int d, int page_size);
 void attention_prefill(const Act &q, const Act &out, const void *kc, const void *vc, const int *seq_start, const int *seq_past,
                        const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int d,
-                       int page_size, int window, int block, float scale, cudaStream_t s, int sink = 0);
+                       int page_size, int window, int block, float scale, cudaStream_t s, int sink = 0, float null_score = NO_NULL_KEY);
 bool attention_prefill_tc_supported(int d, int page_size);
 void attention_prefill_tc(const Act &q, const Act &out, const void *kc, const void *vc, long long n_pages, const int *seq_start,
                           const int *seq_past, const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads,
                           int n_kv, int d, int page_size, int window, int block, float scale, int *status, cudaStream_t s,
-                          int sink = 0);
+                          int sink = 0, float null_score = NO_NULL_KEY);
 // out[t, h, :] *= sigmoid(gate[t * gate_stride + h]) for heads of width dv
 void head_gate(const Act &out, const float *gate, long long gate_stride, int n_heads, int dv, cudaStream_t s);
 // ---- routed feed-forward (csrc/moe.cu)

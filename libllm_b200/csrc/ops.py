@@ -193,8 +193,9 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, 
                       tok_seq: torch.Tensor, tok_pos: torch.Tensor, page_table: torch.Tensor,
                       n_heads: int, n_kv: int, head_dim: int, page_size: int, window: Optional[int],
                       scale: float, v_head_dim: Optional[int] = None, block: Optional[int] = None,
-                      gate: Optional[torch.Tensor] = None, sink: int = 0) -> torch.Tensor:
-    """q is a [T, >= n_heads*d] view whose first n_heads*d columns are the rotated queries.  Values
+                      gate: Optional[torch.Tensor] = None, sink: int = 0, null_score: Optional[float] = None) -> torch.Tensor:
+    """``null_score``: every query also sees one key of that score that has no value.
+    q is a [T, >= n_heads*d] view whose first n_heads*d columns are the rotated queries.  Values
     may have a width of their own; ``block``: a query sees only the keys of its own block of that
     many positions; ``sink``: with a window, the first positions that stay visible; ``gate``
     [T, >= n_heads] 32-bit: head results are multiplied by sigmoid(gate)."""
@@ -205,13 +206,13 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, 
     assert kcache.dtype == q.dtype and out.dtype == q.dtype
     if gate is not None:
         assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == T
-    _call("attention_generic", "llm_attention_generic",
+    _call("attention_generic", "llm_attention_generic_ld",
           [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
-           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_longlong, c_void_p],
+           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_longlong, c_float, c_void_p],
           dtype_code(q.dtype), _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
-          _ptr(tok_seq), _ptr(tok_pos), _ptr(page_table), page_table.stride(0), T, n_heads, n_kv, head_dim, dv,
+          _ptr(tok_seq), _ptr(tok_pos), _ptr(page_table), page_table.stride(0), T, n_heads, n_kv, head_dim, dv, dv,
           page_size, int(window or 0), int(block or 0), int(sink or 0), float(scale), _ptr(gate), gate.stride(0) if gate is not None else 0,
-          _stream())
+          float("-inf") if null_score is None else float(null_score), _stream())
     return out
 
 
@@ -388,7 +389,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, v
                      tok_pos: torch.Tensor, page_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
                      page_size: int, chunk: int, n_splits: int, window: Optional[int], scale: float,
                      ws_o: Optional[torch.Tensor], ws_ml: Optional[torch.Tensor], block: Optional[int] = None,
-                     gate: Optional[torch.Tensor] = None, sink: int = 0, gate_per_channel: bool = False) -> torch.Tensor:
+                     gate: Optional[torch.Tensor] = None, sink: int = 0, gate_per_channel: bool = False,
+                     null_score: Optional[float] = None) -> torch.Tensor:
     """One query token per sequence over the paged cache, keys split into ``n_splits``
     runs of ``chunk``; ``ws_o``/``ws_ml`` are the scratch the splits are joined through."""
     _on_gpu(q, out, kcache, vcache, tok_pos, page_table, ws_o, ws_ml)
@@ -398,13 +400,15 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, v
     if n_splits > 1:
         assert ws_o.dtype == torch.float32 and ws_o.numel() >= B * n_heads * n_splits * head_dim
         assert ws_ml.dtype == torch.float32 and ws_ml.numel() >= B * n_heads * n_splits * 2
-    _call("attention_decode", "llm_attention_decode_sink",
+    _call("attention_decode", "llm_attention_decode_null",
           [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p],
+           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_longlong, c_int,
+           c_float, c_void_p],
           _ptr(q), q.stride(0) if B > 1 else q.shape[1], _ptr(out), out.stride(0) if B > 1 else out.shape[1],
           _ptr(kcache), _ptr(vcache), _ptr(tok_pos), _ptr(page_table), page_table.stride(0), B, n_heads, n_kv,
           head_dim, page_size, chunk, n_splits, int(window or 0), int(block or 0), int(sink or 0), float(scale), _ptr(ws_o), _ptr(ws_ml), _ptr(gate),
-          gate.stride(0) if gate is not None else 0, 1 if gate_per_channel else 0, _stream())
+          gate.stride(0) if gate is not None else 0, 1 if gate_per_channel else 0,
+          float("-inf") if null_score is None else float(null_score), _stream())
     return out
 
 
@@ -419,7 +423,8 @@ def attention_prefill_supported(head_dim: int, page_size: int) -> bool:
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                       seq_start: torch.Tensor, seq_past: torch.Tensor, page_table: torch.Tensor, n_seqs: int,
                       max_q_len: int, n_heads: int, n_kv: int, head_dim: int, page_size: int,
-                      window: Optional[int], scale: float, block: Optional[int] = None, sink: int = 0) -> torch.Tensor:
+                      window: Optional[int], scale: float, block: Optional[int] = None, sink: int = 0,
+                      null_score: Optional[float] = None) -> torch.Tensor:
     """Causal attention of every sequence's new tokens (rows seq_start[b]..seq_start[b+1]-1 of
     ``q``, standing behind seq_past[b] cached tokens) over the paged cache, which already
     holds the new tokens' keys and values."""
@@ -430,12 +435,13 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, 
     assert seq_start.numel() >= n_seqs + 1 and seq_past.numel() >= n_seqs and page_table.shape[0] >= n_seqs
     assert kcache.is_contiguous() and vcache.is_contiguous()
     assert tuple(kcache.shape[1:]) == (n_kv, page_size, head_dim)
-    _call("attention_prefill", "llm_attention_prefill",
+    _call("attention_prefill", "llm_attention_prefill_null",
           [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
           _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(seq_start),
           _ptr(seq_past), _ptr(page_table), page_table.stride(0), n_seqs, max_q_len, n_heads, n_kv, head_dim,
-          page_size, int(window or 0), int(block or 0), int(sink or 0), float(scale), _stream())
+          page_size, int(window or 0), int(block or 0), int(sink or 0), float(scale),
+          float("-inf") if null_score is None else float(null_score), _stream())
     return out
 
 
@@ -608,7 +614,7 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
                          seq_start: torch.Tensor, seq_past: torch.Tensor, page_table: torch.Tensor, n_seqs: int,
                          max_q_len: int, n_heads: int, n_kv: int, head_dim: int, page_size: int,
                          window: Optional[int], scale: float, form: int = 0, block: Optional[int] = None,
-                         sink: int = 0) -> torch.Tensor:
+                         sink: int = 0, null_score: Optional[float] = None) -> torch.Tensor:
     """The same attention as ``attention_prefill`` with both products on tcgen05 (head sizes 64, 128).
     ``form``: 1 for CTAs of 128 query rows and tiles of 64 keys, 2 for CTAs of 256 rows and tiles of
     128 keys, 0 for the library's choice (the second when a sequence brings more than 128 rows)."""
@@ -617,12 +623,13 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == q.shape[0]
     assert seq_start.dtype == torch.int32 and seq_past.dtype == torch.int32 and page_table.dtype == torch.int32
     assert kcache.is_contiguous() and vcache.is_contiguous() and tuple(kcache.shape[1:]) == (n_kv, page_size, head_dim)
-    _call("attention_prefill_tc", "llm_attention_prefill_tc",
+    _call("attention_prefill_tc", "llm_attention_prefill_tc_null",
           [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
-           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p],
           _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), kcache.shape[0],
           _ptr(seq_start), _ptr(seq_past), _ptr(page_table), page_table.stride(0), n_seqs, max_q_len, n_heads, n_kv,
-          head_dim, page_size, int(window or 0), int(block or 0), int(sink or 0), float(scale), int(form), _ptr(tc_status(q.device)), _stream())
+          head_dim, page_size, int(window or 0), int(block or 0), int(sink or 0), float(scale),
+          float("-inf") if null_score is None else float(null_score), int(form), _ptr(tc_status(q.device)), _stream())
     return out
 
 
@@ -705,3 +712,66 @@ def head_norm_gate(x: torch.Tensor, weight: Optional[torch.Tensor], gate: Option
           _ptr(x), x.stride(0), _ptr(weight), _ptr(gate), gate.stride(0) if gate is not None else 0, float(eps), x.shape[0], n_heads,
           dv, _ptr(out), dtype_code(out.dtype), out.stride(0), _stream())
     return out
+
+
+# ---------------------------------------------------------------- several residual streams, unit heads, routing among groups
+def hyper_mix_norm(x: torch.Tensor, delta: Optional[torch.Tensor], mix: Optional[torch.Tensor], outw: Optional[torch.Tensor],
+                   inw: Optional[torch.Tensor], norm_w: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor],
+                   rows: Optional[torch.Tensor] = None, x_out: Optional[torch.Tensor] = None, spread: bool = True) -> None:
+    """x [S, T, H] 32-bit copies of the residual stream (``spread`` false: only copy 0 is read, the others count as equal
+    to it).  Applies the pending result ``delta`` [T, H] or [parts, T, H] (x_t <- sum_s mix[s, t] x_s + outw[t] y), stores
+    the copies (in place, or the chosen ``rows`` to ``x_out`` [S, n, H]), then out = rmsnorm(sum_s inw[s] x_s) * norm_w, or
+    the joined rows themselves in 32-bit when ``norm_w`` is None (``inw`` None: the plain sum)."""
+    _on_gpu(x, delta, mix, outw, inw, norm_w, out, rows, x_out)
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 3
+    S, T, H = x.shape
+    n_parts, stride = 0, 0
+    if delta is not None:
+        assert delta.dtype == torch.float32 and delta.is_contiguous() and tuple(delta.shape[-2:]) == (T, H)
+        n_parts = 1 if delta.dim() == 2 else delta.shape[0]
+        stride = T * H
+    n_rows = T if rows is None else rows.numel()
+    dst = x if x_out is None and rows is None else x_out
+    if dst is not None and dst is not x:
+        assert dst.dtype == torch.float32 and dst.is_contiguous() and tuple(dst.shape) == (S, n_rows, H)
+    _call("elementwise", "llm_hyper_mix_norm",
+          [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+           c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+          _ptr(x), T * H if spread else 0, _ptr(dst), n_rows * H if dst is not x else T * H, S, _ptr(delta), n_parts, stride, None, None,
+          _ptr(mix), _ptr(outw), _ptr(inw), _ptr(norm_w), float(eps), _ptr(out), F32 if out is None else dtype_code(out.dtype),
+          _ptr(rows), n_rows, H, _stream())
+
+
+def rope_headnorm_place(qkv: torch.Tensor, q_out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, v_head_dim: int, eps: float,
+                        table: Optional[torch.Tensor], tok_seq: torch.Tensor, tok_pos: torch.Tensor, page_table: torch.Tensor,
+                        kcache: torch.Tensor, vcache: torch.Tensor, page_size: int, write_cache: bool = True) -> None:
+    """Rows [q | k | v | ...]: rotation of the first ``table.shape[1]`` channels of each q and k head (pairs i, i + half), then
+    every head divided by its root mean square (``eps`` < 0: no norm); q to ``q_out``, k and v to the paged cache."""
+    _on_gpu(qkv, q_out, table, tok_seq, tok_pos, page_table, kcache, vcache)
+    assert qkv.stride(1) == 1 and q_out.stride(1) == 1
+    _call("rope", "llm_rope_headnorm_place",
+          [c_int, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int,
+           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+          dtype_code(qkv.dtype), dtype_code(q_out.dtype), _ptr(qkv), qkv.stride(0), _ptr(q_out), q_out.stride(0), qkv.shape[0], n_heads,
+          n_kv, head_dim, v_head_dim, float(eps), _ptr(table), 0 if table is None else table.shape[0], 0 if table is None else table.shape[1],
+          _ptr(tok_seq), _ptr(tok_pos), _ptr(page_table), page_table.stride(0), _ptr(kcache), _ptr(vcache), page_size,
+          1 if write_cache else 0, _stream())
+
+
+def moe_route_grouped(logits: torch.Tensor, top: int, correction: Optional[torch.Tensor] = None, n_groups: int = 1, keep: int = 1,
+                      group_top: int = 2, score: str = "sigmoid", renormalize: bool = True, norm_eps: float = 0.0,
+                      route_scale: float = 1.0):
+    """(chosen [T, top] int32, weight [T, top] float32): the choice on score + correction among the experts of the ``keep``
+    best of ``n_groups`` groups, the weights from the scores as they are."""
+    _on_gpu(logits, correction)
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == E)
+    chosen = torch.empty(T, top, dtype=torch.int32, device=logits.device)
+    weight = torch.empty(T, top, dtype=torch.float32, device=logits.device)
+    _call("moe", "llm_moe_route_grouped",
+          [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p,
+           c_void_p],
+          _ptr(logits), logits.stride(0), T, E, top, {"sigmoid": 0, "softmax": 1}[score], _ptr(correction), n_groups, keep, group_top,
+          1 if renormalize else 0, float(norm_eps), float(route_scale), _ptr(chosen), _ptr(weight), _stream())
+    return chosen, weight

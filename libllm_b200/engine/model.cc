@@ -224,8 +224,9 @@ Act Model::forward(StepContext &ctx, KVCache &cache, const std::vector<const int
   }
   ctx.rows_read_after = nullptr;
   ctx.nothing_read_after = false;
-  if (stream.streams > 1) {
+  if (stream.streams > 1 || stream.pending_mix) {
     // the last norm reads the sum of the copies, at the wanted rows: the last sublayer's result is applied on the way
+    // (with one copy too: its result may be waiting with a matrix and a vector of its own)
     flush_chain(ctx);
     const int64_t n = stream.picked ? stream.rows : ctx.n_want;
     float *sum = ctx.arena->alloc_n<float>((size_t)(n * H));

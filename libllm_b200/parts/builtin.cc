@@ -41,7 +41,8 @@ class RMSNorm : public Norm {
     return true;
   }
   Act forward(StepContext &ctx, ResidualStream &stream, const int *rows, int n_rows) override {
-    if (stream.streams > 1) LLM_THROW(InvalidArg, "rmsnorm: the residual stream has %d copies; the block that keeps them joins them first", stream.streams);
+    if (stream.streams > 1 || stream.pending_mix)
+      LLM_THROW(InvalidArg, "rmsnorm: the residual stream has %d copies (or a result waiting to move them); the block that keeps them joins them first", stream.streams);
     const int64_t n = rows ? n_rows : stream.rows;
     Act out = ctx.arena->act(ctx.dtype, n, size_);
     if (ctx.chain && ctx.dtype == DType::BF16 &&
@@ -515,7 +516,7 @@ class Attention : public Mixer {
     // a gate per channel is applied behind the attention kernel, whichever it is
     const float *channel_gate = gate_per_channel_ ? gate : nullptr;
     if (gate_per_channel_) gate = nullptr;
-    if (ctx.dtype == DType::BF16 && plain_ && !has_null) {
+    if (ctx.dtype == DType::BF16 && plain_) {
       if (ctx.decode_only && f.decode_attention && kernels::available("attention_decode") &&
           kernels::attention_decode_supported(d_, group)) {
         // enough CTAs to fill the GPU about eight times over at the longest length, runs of at
@@ -535,7 +536,7 @@ class Attention : public Mixer {
         }
         kernels::attention_decode(q, out, cache->k, cache->v, ctx.tok_pos, cache->page_table, cache->table_width, n_heads_, n_kv_,
                                   d_, cache->page_size, chunk, n_splits, window_, block_, scale_, ws_o, ws_ml,
-                                  channel_gate ? channel_gate : gate, qkv.ld, ctx.stream, sink_, channel_gate != nullptr);
+                                  channel_gate ? channel_gate : gate, qkv.ld, ctx.stream, sink_, channel_gate != nullptr, null_score_);
         gate = nullptr;                 // applied
         channel_gate = nullptr;
         done = true;
@@ -543,13 +544,13 @@ class Attention : public Mixer {
                  kernels::attention_prefill_tc_supported(d_, cache->page_size)) {
         kernels::attention_prefill_tc(q, out, cache->k, cache->v, cache->n_pages, ctx.seq_start, ctx.seq_past, cache->page_table,
                                       cache->table_width, ctx.n_seqs, ctx.max_q_len, n_heads_, n_kv_, d_, cache->page_size, window_,
-                                      block_, scale_, ctx.tc_status, ctx.stream, sink_);
+                                      block_, scale_, ctx.tc_status, ctx.stream, sink_, null_score_);
         done = true;
       } else if (f.prefill_attention && kernels::available("attention_prefill") &&
                  kernels::attention_prefill_supported(d_, cache->page_size)) {
         kernels::attention_prefill(q, out, cache->k, cache->v, ctx.seq_start, ctx.seq_past, cache->page_table, cache->table_width,
                                    ctx.n_seqs, ctx.max_q_len, n_heads_, n_kv_, d_, cache->page_size, window_, block_, scale_, ctx.stream,
-                                   sink_);
+                                   sink_, null_score_);
         done = true;
       }
       if (done && gate) kernels::head_gate(out, gate, qkv.ld, n_heads_, dv_, ctx.stream);
