@@ -575,6 +575,104 @@ def run_compare_sobezen(args):
     return 0
 
 
+# ---------------------------------------------------------------- Tazizen beside Llama at equal sizes
+def tazizen_config(hidden, runs, heads, kv, dim, ff, vocab, streams=4, window=1024, kv_rank=512, experts=32, top=4):
+    """A Tazizen model of `runs` layers in the order latent attention, latent attention, attention, every layer with the
+    routed feed-forward: `experts` experts of ff / 8 of which `top` (4: half of ff) are chosen among the better half of
+    four groups, and a shared expert of ff / 2, so that a token uses as many feed-forward values as Llama's dense one.
+    `streams` copies of the residual stream; windows of `window` positions everywhere.  The latent layers' heads have
+    `dim` unrotated and dim / 2 rotated channels and a query latent of 3 / 8 of the width."""
+    rot = dict(dims=dim, base=1e4, scaling=dict(factor=4.0, original=2048, fast=32.0, slow=1.0))
+    rot_l = dict(dims=dim // 2, base=1e6)
+    mlp = dict(kind="moe", expert=dict(ff=ff // 8), shared=dict(ff=ff // 2),
+               router=dict(experts=experts, top=top, scale=1.5, groups=dict(count=4, keep=2)))
+    layers = []
+    for i in range(runs):
+        if i % 3 == 2:
+            L = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv, dim=dim, vdim=dim, scale=dim ** -0.5, rot=rot, mask=dict(size=window)))
+        else:
+            L = dict(type="latent_attention", mixer=dict(heads=heads, dim=dim, rot_dim=dim // 2, vdim=dim, kv_rank=kv_rank, q_rank=hidden * 3 // 8,
+                                                         scale=(dim + dim // 2) ** -0.5, rot=rot_l, mask=dict(size=window)))
+        layers.append(dict(mlp=mlp, **L))
+    return dict(architecture="Tazizen", vocab=vocab, width=hidden, norm=dict(eps=1e-5), streams=streams, layers=layers)
+
+
+def tazizen_numbers(c, batch):
+    """(bytes a decode step of `batch` sequences reads apart from the cache, cache bytes per visible token and layer kind
+    as a function of the context, prefill flops of T tokens with one wanted row)."""
+    H, V = c["width"], c["vocab"]
+    used, touched, per_key = 0, 0, []                 # matrix values a token uses / a decode step can touch
+    for L in c["layers"]:
+        m = L["mixer"]
+        window = (m.get("mask") or {}).get("size") or (1 << 30)
+        if L["type"] == "attention":
+            mats = H * (m["heads"] * (m["dim"] + m["vdim"]) + m["kv_heads"] * (m["dim"] + m["vdim"])) + m["heads"] * m["vdim"] * H
+            per_key.append((window, 2 * m["kv_heads"] * (m["dim"] + m["vdim"]), 2 * m["heads"] * (m["dim"] + m["vdim"])))
+        else:
+            row = m["kv_rank"] + m["rot_dim"]
+            mats = H * m["q_rank"] + m["q_rank"] * m["heads"] * (m["dim"] + m["rot_dim"]) + m["heads"] * (m["dim"] + m["vdim"]) * m["kv_rank"]
+            mats += m["heads"] * m["vdim"] * H + H * row
+            per_key.append((window, 2 * row, 2 * m["heads"] * (row + m["kv_rank"])))
+        used += mats
+        touched += mats
+        f = L["mlp"]
+        if f:
+            r, one = f["router"], 3 * H * f["expert"]["ff"]
+            shared = 3 * H * f["shared"]["ff"] + H if f.get("shared") else 0
+            used += r["experts"] * H + r["top"] * one + shared
+            touched += r["experts"] * H + min(r["experts"], batch * r["top"]) * one + shared
+    weight_bytes = 2 * (touched + V * H)
+
+    def cache_bytes(ctx_len):
+        return sum(b * min(ctx_len, w) for w, b, _ in per_key)
+
+    def prefill_flops(T):
+        att = sum(fl * sum(min(p + 1, w) for p in range(T)) for w, _, fl in per_key)
+        return 2 * T * used + att + 2 * V * H
+    return weight_bytes, cache_bytes, prefill_flops
+
+
+def run_compare_tazizen(args):
+    """Prefill and decode of Tazizen beside Llama, both with random weights, at equal hidden size, number of layers,
+    heads, head size, feed-forward values used per token and vocabulary: one JSON line per size and model."""
+    import torch
+    from libllm_b200 import Model
+    pk = peaks()
+    names = [n for n in SOBEZEN_SIZES if not args.sizes or n in args.sizes.split(",")]
+    for name in names:
+        hidden, runs, heads, kv, dim, ff, vocab = SOBEZEN_SIZES[name]
+        llama = dict(LLAMA_1B, num_hidden_layers=runs, hidden_size=hidden, num_attention_heads=heads, num_key_value_heads=kv,
+                     head_dim=dim, intermediate_size=ff, vocab_size=vocab, tie_word_embeddings=False, rope_scaling=None)
+        zen = tazizen_config(hidden, runs, heads, kv, dim, ff, vocab)
+        for label, cfg in (("llama", llama), ("tazizen", zen)):
+            if args.model and args.model != label:
+                continue
+            if label == "llama":
+                wbytes, kv_per_tok, flops_fn = model_numbers(cfg)
+                cache_fn = lambda n: n * kv_per_tok
+            else:
+                wbytes, cache_fn, flops_fn = tazizen_numbers(cfg, args.batch)
+            flops = flops_fn(PROMPT)
+            model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=args.batch * CONTEXT, max_seq_len=CONTEXT)
+            pre = prefill_rate(model, vocab, lambda T: flops, pk["bf16_tflops"])
+            rate, ms, ctx_len, launches = decode_rate(model, args.batch, args.steps, args.warmup, vocab)
+            step_bytes = wbytes + args.batch * cache_fn(ctx_len)
+            print(json.dumps({"compare": name, "model": label, "batch": args.batch, "prompt": PROMPT,
+                              "config": {"hidden": hidden, "layers": runs, "heads": heads, "kv_heads": kv, "head_dim": dim, "ff": ff,
+                                         "vocab": vocab, "order": [L["type"] for L in zen["layers"]] if label == "tazizen" else None,
+                                         "streams": zen["streams"] if label == "tazizen" else None},
+                              "prefill": {"ms": round(pre["ms"], 3), "tok_s": round(pre["value"], 1), "tflop": round(flops / 1e12, 3),
+                                          "frac_of_gemm_peak": round(pre["frac"], 4)},
+                              "decode": {"tok_s": round(rate, 1), "ms_per_step": round(ms, 4), "launches_per_step": launches,
+                                         "step_gb": round(step_bytes / 1e9, 3),
+                                         "hbm_frac": round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)},
+                              "peaks": pk["source"]}), flush=True)
+            model.engine.close()
+            del model
+            torch.cuda.empty_cache()
+    return 0
+
+
 def run_compare(args):
     """Prefill and decode of Sinezen beside Llama, both with random weights, at equal hidden size, layer
     runs, heads, head size, feed-forward width (with experts: equal matrix values used per token) and
@@ -689,9 +787,10 @@ def main():
                     help="1b: the benchmark line (default); 3b, 8b: the larger workloads, a line of their own")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print a short line (for profiling; not a bench record)")
-    ap.add_argument("--compare", choices=["sinezen", "sesuzen", "sobezen"], default=None,
-                    help="Sinezen, Sesuzen or Sobezen beside Llama at equal sizes: prefill and decode, a line per size and model (not a bench record)")
-    ap.add_argument("--model", choices=["llama", "sesuzen", "sobezen"], default=None, help="with --compare sesuzen or sobezen: one of the two models only")
+    ap.add_argument("--compare", choices=["sinezen", "sesuzen", "sobezen", "tazizen"], default=None,
+                    help="Sinezen, Sesuzen, Sobezen or Tazizen beside Llama at equal sizes: prefill and decode, a line per size and model (not a bench record)")
+    ap.add_argument("--model", choices=["llama", "sesuzen", "sobezen", "tazizen"], default=None,
+                    help="with --compare sesuzen, sobezen or tazizen: one of the two models only")
     ap.add_argument("--sizes", default=None, help="with --compare: which of the sizes (2k, 4k, 2k-routed), with commas")
     ap.add_argument("--prompt-len", type=int, default=None,
                     help="with --only: prompts of this many tokens instead of 2048 (the context grows to fit)")
@@ -713,6 +812,8 @@ def main():
         return run_compare_sesuzen(args)
     if args.compare == "sobezen":
         return run_compare_sobezen(args)
+    if args.compare == "tazizen":
+        return run_compare_tazizen(args)
     if args.compare:
         return run_compare(args)
     if args.workload != "1b":
