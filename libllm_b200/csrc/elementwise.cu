@@ -1176,7 +1176,13 @@ static int launch_hyper(const float *x_in, long long in_stride, float *x_out, lo
   LLM_REQUIRE(smem <= 200 * 1024, "hyper_mix_norm: a row of %d values does not fit shared memory", hidden);
   const bool vec = hidden % 4 == 0 && in_stride % 4 == 0 && out_stride % 4 == 0 && part_stride % 4 == 0 && (uintptr_t)x_in % 16 == 0 &&
                    (uintptr_t)x_out % 16 == 0 && (uintptr_t)delta % 16 == 0;
-  if (vec) {
+  if (vec && hidden >= 2048) {
+    // wide rows: 512 threads, so that a row of 2,048 values is one round of loads per thread
+    auto kern = hyper_mix_norm_kernel<TO, 512, 4>;
+    LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "hyper_mix_norm attribute");
+    llm_launch(kern, dim3(n_rows), dim3(512), smem, stream, x_in, in_stride, x_out, out_stride, S, delta, n_parts, part_stride, col_scale,
+               col_bias, mix, outw, inw, norm_w, eps, out, rows, hidden);
+  } else if (vec) {
     auto kern = hyper_mix_norm_kernel<TO, 256, 4>;
     LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "hyper_mix_norm attribute");
     llm_launch(kern, dim3(n_rows), dim3(256), smem, stream, x_in, in_stride, x_out, out_stride, S, delta, n_parts, part_stride, col_scale,

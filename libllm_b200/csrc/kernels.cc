@@ -509,14 +509,15 @@ LLM_KERNEL("moe", llm_activation, int, int, const void *, void *, long long, int
 LLM_KERNEL("moe", llm_moe_route, const float *, long long, int, int, int, int, int, int *, float *, cudaStream_t)
 LLM_KERNEL("moe", llm_moe_route_grouped, const float *, long long, int, int, int, int, const float *, int, int, int, int, float, float,
            int *, float *, cudaStream_t)
-LLM_KERNEL("moe", llm_row_gate, const float *, float *, const float *, long long, int, int, cudaStream_t)
+LLM_KERNEL("moe", llm_row_gate, const float *, long long, float *, long long, int, const float *, long long, int, int, cudaStream_t)
 void moe_route_grouped(const Act &logits, int n_experts, int top, int score, const float *correction, int n_groups, int keep,
                        int group_top, bool renormalize, float norm_eps, float route_scale, int *chosen, float *weight, cudaStream_t s) {
   LLM_CALL("moe", llm_moe_route_grouped, (const float *)logits.data, (long long)logits.ld, (int)logits.rows, n_experts, top, score,
            correction, n_groups, keep, group_top, renormalize ? 1 : 0, norm_eps, route_scale, chosen, weight, s);
 }
-void row_gate(const float *x, float *out, const float *gate, long long gate_stride, int n_rows, int cols, cudaStream_t s) {
-  LLM_CALL("moe", llm_row_gate, x, out, gate, gate_stride, n_rows, cols, s);
+void row_gate(const float *x, long long x_stride, float *out, long long out_stride, int n_parts, const float *gate,
+              long long gate_stride, int n_rows, int cols, cudaStream_t s) {
+  LLM_CALL("moe", llm_row_gate, x, x_stride, out, out_stride, n_parts, gate, gate_stride, n_rows, cols, s);
 }
 LLM_KERNEL("moe", llm_moe_sort, const int *, int, int, int, int *, int *, int *, cudaStream_t)
 LLM_KERNEL("moe", llm_moe_rows, int, const void *, long long, const void *, const void *, const int *, const float *, int, int, int,

@@ -187,8 +187,9 @@ void moe_route(const Act &logits, int n_experts, int top, int score, bool renorm
 // its group_top largest corrected scores); weights s, with `renormalize` s / (sum + norm_eps), times route_scale.
 void moe_route_grouped(const Act &logits, int n_experts, int top, int score, const float *correction, int n_groups, int keep,
                        int group_top, bool renormalize, float norm_eps, float route_scale, int *chosen, float *weight, cudaStream_t s);
-// out[t, :] = x[t, :] * sigmoid(gate[t * gate_stride]), 32-bit rows
-void row_gate(const float *x, float *out, const float *gate, long long gate_stride, int n_rows, int cols, cudaStream_t s);
+// out[p, t, :] = x[p, t, :] * sigmoid(gate[t * gate_stride]) for n_parts parts, 32-bit rows
+void row_gate(const float *x, long long x_stride, float *out, long long out_stride, int n_parts, const float *gate,
+              long long gate_stride, int n_rows, int cols, cudaStream_t s);
 int moe_tile_rows();
 void moe_sort(const int *chosen, int n_rows, int n_experts, int tile_rows, int *offsets, int *perm, int *tiles, cudaStream_t s);
 // x [T, width]; up [E, ff, width], down [E, width, ff] in x's type; out [top, T, width] 32-bit.  `gated`: up is

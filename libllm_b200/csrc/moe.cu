@@ -245,24 +245,28 @@ LLM_EXPORT int llm_moe_route_grouped(const float *logits, long long ld, int n_to
   return LLM_OK;
 }
 
-// out[t, :] = x[t, :] * sigmoid(gate[t * gate_stride]) (32-bit rows): a feed-forward's result weighed by one number per token.
-__global__ void row_gate_kernel(const float *__restrict__ x, float *__restrict__ out, const float *__restrict__ gate,
-                                long long gate_stride, int cols, long long total) {
+// out[p, t, :] = x[p, t, :] * sigmoid(gate[t * gate_stride]) for every part p (32-bit rows; parts x_stride and out_stride
+// floats apart): a feed-forward's result, whole or in partial products, weighed by one number per token.
+__global__ void row_gate_kernel(const float *__restrict__ x, long long x_stride, float *__restrict__ out, long long out_stride,
+                                const float *__restrict__ gate, long long gate_stride, int cols, long long total) {
   grid_dependents_launch();
   grid_dependency_wait();
+  const float *xp = x + (size_t)blockIdx.y * x_stride;
+  float *op = out + (size_t)blockIdx.y * out_stride;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long t = i / cols;
-    out[i] = x[i] * (1.f / (1.f + expf(-gate[t * gate_stride])));
+    op[i] = xp[i] * (1.f / (1.f + expf(-gate[t * gate_stride])));
   }
 }
-LLM_EXPORT int llm_row_gate(const float *x, float *out, const float *gate, long long gate_stride, int n_rows, int cols,
-                            cudaStream_t stream) {
-  if (n_rows == 0 || cols == 0) return LLM_OK;
-  LLM_REQUIRE(n_rows > 0 && cols > 0 && x && out && gate, "row_gate: bad arguments");
+LLM_EXPORT int llm_row_gate(const float *x, long long x_stride, float *out, long long out_stride, int n_parts, const float *gate,
+                            long long gate_stride, int n_rows, int cols, cudaStream_t stream) {
+  if (n_rows == 0 || cols == 0 || n_parts == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && cols > 0 && n_parts > 0 && n_parts <= 65535 && x && out && gate, "row_gate: bad arguments");
   const long long total = (long long)n_rows * cols;
   long long blocks = (total + 255) / 256;
   if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
-  llm_launch(row_gate_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, out, gate, gate_stride, cols, total);
+  llm_launch(row_gate_kernel, dim3((unsigned)blocks, (unsigned)n_parts), dim3(256), 0, stream, x, x_stride, out, out_stride, gate,
+             gate_stride, cols, total);
   LLM_CHECK_LAUNCH("row_gate");
   return LLM_OK;
 }

@@ -578,11 +578,12 @@ LLM_EXPORT int llm_rope_pairs_place(int in_dtype, int dtype, const void *qkv, lo
 //   carry a factor on cosines and sines alike), then head <- head / sqrt(mean(head^2) + eps) over its d channels
 //   (eps < 0: no norm), q -> q_out, k and v -> the token's row of the paged cache; values of width dv as they are.
 // A row of the stacked product is [q: n_heads * d | k: n_kv * d | v: n_kv * dv | anything else].  One CTA per
-// token, a warp per head in turn; a head's channels stay in registers between the rotation and the norm
-// (d <= 512).  Angles come from the table (computed in 64-bit, rounded once); sums and factors are 32-bit and
+// token, a few lanes per head; a head's channels stay in registers between the rotation and the norm
+// (d - rot_dim/2 <= 512).  Angles come from the table (computed in 64-bit, rounded once); sums and factors are 32-bit and
 // a head's sum has a fixed order.
-constexpr int HN_MAX_ITEMS = 16;          // items of a lane: d - rot_dim/2 <= 32 * HN_MAX_ITEMS
-template <typename TI, typename T>
+// LANES lanes share a head (8, 16 or 32: the fewer, the more heads a warp has in flight at once), ITEMS items each; an
+// item is V consecutive pairs (or unrotated channels): V = 4 where the widths are multiples of 4 and rows lie on 16 bytes.
+template <typename TI, typename T, int LANES, int ITEMS, int V>
 __global__ void __launch_bounds__(256)
 rope_headnorm_place_kernel(const TI *__restrict__ qkv, long long row_stride, T *__restrict__ q_out, long long q_stride, int n_heads,
                            int n_kv, int d, int dv, float eps, const float *__restrict__ table, int table_rows, int rot_dim,
@@ -590,7 +591,9 @@ rope_headnorm_place_kernel(const TI *__restrict__ qkv, long long row_stride, T *
                            int pt_stride, T *__restrict__ kcache, T *__restrict__ vcache, int page_size, int write_cache) {
   grid_dependents_launch();
   grid_dependency_wait();
+  constexpr int PER_WARP = 32 / LANES;
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane % LANES, group = lane / LANES;
   const int pos = tok_pos[t];
   const TI *row = qkv + (size_t)t * row_stride;
   const int qw = n_heads * d, kw = n_kv * d;
@@ -603,49 +606,85 @@ rope_headnorm_place_kernel(const TI *__restrict__ qkv, long long row_stride, T *
   const float *cs = table ? table + (size_t)(pos < table_rows ? pos : table_rows - 1) * rot_dim : nullptr;
   const int per_head = d - half;               // `half` pairs, then the channels that are not rotated
   const int n_slots = n_heads + (write_cache ? n_kv : 0);
-  for (int slot = warp; slot < n_slots; slot += 8) {
+  // every lane of a warp goes through the same number of rounds: the shuffles below are the whole warp's
+  for (int base = warp * PER_WARP; base < n_slots; base += 8 * PER_WARP) {
+    const int slot = base + group;
+    const bool live = slot < n_slots;
     const bool is_q = slot < n_heads;
-    const TI *src = row + (size_t)slot * d;
-    T *dst = is_q ? q_out + (size_t)t * q_stride + (size_t)slot * d : kcache + (cache_row + (size_t)(slot - n_heads) * page_size) * d;
-    float a[HN_MAX_ITEMS], b[HN_MAX_ITEMS];
+    const TI *src = row + (size_t)(live ? slot : 0) * d;
+    float a[ITEMS][V], b[ITEMS][V];
     float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < HN_MAX_ITEMS; ++k) {
-      const int i = lane + 32 * k;
-      a[k] = b[k] = 0.f;
-      if (i < per_head) {
+    for (int k = 0; k < ITEMS; ++k) {
+      const int i = (sub + LANES * k) * V;
+#pragma unroll
+      for (int e = 0; e < V; ++e) a[k][e] = b[k][e] = 0.f;
+      if (live && i < per_head) {
         if (i < half) {
-          const float u = to_float(src[i]), v = to_float(src[i + half]);
-          const float c = cs[i], s = cs[half + i];
-          a[k] = u * c - v * s;
-          b[k] = v * c + u * s;
+          float u[V], v[V], c[V], sn[V];
+          if (V == 4) {
+            const float4 u4 = ld4(src + i), v4 = ld4(src + i + half), c4 = ld4(cs + i), s4 = ld4(cs + half + i);
+            u[0] = u4.x, u[1 % V] = u4.y, u[2 % V] = u4.z, u[3 % V] = u4.w;
+            v[0] = v4.x, v[1 % V] = v4.y, v[2 % V] = v4.z, v[3 % V] = v4.w;
+            c[0] = c4.x, c[1 % V] = c4.y, c[2 % V] = c4.z, c[3 % V] = c4.w;
+            sn[0] = s4.x, sn[1 % V] = s4.y, sn[2 % V] = s4.z, sn[3 % V] = s4.w;
+          } else {
+            u[0] = to_float(src[i]), v[0] = to_float(src[i + half]), c[0] = cs[i], sn[0] = cs[half + i];
+          }
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            a[k][e] = u[e] * c[e] - v[e] * sn[e];
+            b[k][e] = v[e] * c[e] + u[e] * sn[e];
+          }
         } else {
-          a[k] = to_float(src[i + half]);
+          if (V == 4) {
+            const float4 u4 = ld4(src + i + half);
+            a[k][0] = u4.x, a[k][1 % V] = u4.y, a[k][2 % V] = u4.z, a[k][3 % V] = u4.w;
+          } else {
+            a[k][0] = to_float(src[i + half]);
+          }
         }
-        ss = fmaf(a[k], a[k], ss);
-        ss = fmaf(b[k], b[k], ss);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          ss = fmaf(a[k][e], a[k][e], ss);
+          ss = fmaf(b[k][e], b[k][e], ss);
+        }
       }
     }
-    float fac = 1.f;
-    if (eps >= 0.f) fac = 1.f / sqrtf(warp_sum(ss) / (float)d + eps);
 #pragma unroll
-    for (int k = 0; k < HN_MAX_ITEMS; ++k) {
-      const int i = lane + 32 * k;
+    for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float fac = eps >= 0.f ? 1.f / sqrtf(ss / (float)d + eps) : 1.f;
+    if (!live) continue;
+    T *dst = is_q ? q_out + (size_t)t * q_stride + (size_t)slot * d : kcache + (cache_row + (size_t)(slot - n_heads) * page_size) * d;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const int i = (sub + LANES * k) * V;
       if (i < per_head) {
-        if (i < half) {
-          dst[i] = from_float<T>(a[k] * fac);
-          dst[i + half] = from_float<T>(b[k] * fac);
+        if (V == 4) {
+          st4(dst + (i < half ? i : i + half), make_float4(a[k][0] * fac, a[k][1 % V] * fac, a[k][2 % V] * fac, a[k][3 % V] * fac));
+          if (i < half) st4(dst + i + half, make_float4(b[k][0] * fac, b[k][1 % V] * fac, b[k][2 % V] * fac, b[k][3 % V] * fac));
+        } else if (i < half) {
+          dst[i] = from_float<T>(a[k][0] * fac);
+          dst[i + half] = from_float<T>(b[k][0] * fac);
         } else {
-          dst[i + half] = from_float<T>(a[k] * fac);
+          dst[i + half] = from_float<T>(a[k][0] * fac);
         }
       }
     }
   }
   if (write_cache) {
     const TI *vsrc = row + qw + kw;
-    for (int item = threadIdx.x; item < n_kv * dv; item += 256) {
-      const int kvh = item / dv, ch = item - kvh * dv;
-      vcache[(cache_row + (size_t)kvh * page_size) * dv + ch] = from_float<T>(to_float(vsrc[item]));
+    if (V == 4) {
+      const int dv4 = dv / 4;
+      for (int item = threadIdx.x; item < n_kv * dv4; item += 256) {
+        const int kvh = item / dv4, ch = (item - kvh * dv4) * 4;
+        st4(vcache + (cache_row + (size_t)kvh * page_size) * dv + ch, ld4(vsrc + (size_t)kvh * dv + ch));
+      }
+    } else {
+      for (int item = threadIdx.x; item < n_kv * dv; item += 256) {
+        const int kvh = item / dv, ch = item - kvh * dv;
+        vcache[(cache_row + (size_t)kvh * page_size) * dv + ch] = from_float<T>(to_float(vsrc[item]));
+      }
     }
   }
 }
@@ -658,16 +697,31 @@ LLM_EXPORT int llm_rope_headnorm_place(int in_dtype, int dtype, const void *qkv,
   LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && d > 0 && dv > 0, "rope_headnorm_place: bad sizes");
   LLM_REQUIRE(rot_dim % 2 == 0 && rot_dim <= d && rot_dim >= 0 && (rot_dim == 0 || table != nullptr),
               "rope_headnorm_place: rotated width %d does not fit head size %d", rot_dim, d);
-  LLM_REQUIRE(d - rot_dim / 2 <= 32 * HN_MAX_ITEMS, "rope_headnorm_place: heads of %d channels are not supported", d);
+  const int per_head = d - rot_dim / 2;
+  LLM_REQUIRE(per_head <= 32 * 16, "rope_headnorm_place: heads of %d channels are not supported", d);
   LLM_REQUIRE(row_stride >= (long long)n_heads * d + (long long)n_kv * (d + dv), "rope_headnorm_place: the stacked rows are too short");
-#define HN_PLACE(TI, T)                                                                                                       \
-  llm_launch(rope_headnorm_place_kernel<TI, T>, dim3(n_tokens), dim3(256), 0, stream, (const TI *)qkv, row_stride, (T *)q_out, \
-             q_stride, n_heads, n_kv, d, dv, eps, table, table_rows, rot_dim, tok_seq, tok_pos, page_table, pt_stride,       \
-             (T *)kcache, (T *)vcache, page_size, write_cache)
+  // four channels to a load where every width is a multiple of 4 and every row starts on 16 bytes
+  const bool vec = d % 4 == 0 && dv % 4 == 0 && rot_dim % 8 == 0 && row_stride % 4 == 0 && q_stride % 4 == 0 && (uintptr_t)qkv % 16 == 0 &&
+                   (uintptr_t)q_out % 16 == 0 && (uintptr_t)table % 16 == 0 && (uintptr_t)kcache % 16 == 0 && (uintptr_t)vcache % 16 == 0 &&
+                   ((long long)n_heads * d) % 4 == 0 && ((long long)n_kv * d) % 4 == 0;
+#define HN_GO(TI, T, LANES, ITEMS, V)                                                                                            \
+  llm_launch(rope_headnorm_place_kernel<TI, T, LANES, ITEMS, V>, dim3(n_tokens), dim3(256), 0, stream, (const TI *)qkv, row_stride, \
+             (T *)q_out, q_stride, n_heads, n_kv, d, dv, eps, table, table_rows, rot_dim, tok_seq, tok_pos, page_table,            \
+             pt_stride, (T *)kcache, (T *)vcache, page_size, write_cache)
+#define HN_PLACE(TI, T)                                                \
+  do {                                                                 \
+    if (vec && per_head <= 64) HN_GO(TI, T, 8, 2, 4);                  \
+    else if (vec && per_head <= 128) HN_GO(TI, T, 16, 2, 4);           \
+    else if (vec) HN_GO(TI, T, 32, 4, 4);                              \
+    else if (per_head <= 64) HN_GO(TI, T, 8, 8, 1);                    \
+    else if (per_head <= 128) HN_GO(TI, T, 16, 8, 1);                  \
+    else HN_GO(TI, T, 32, 16, 1);                                      \
+  } while (0)
   if (in_dtype == LLM_F32 && dtype == LLM_F32) HN_PLACE(float, float);
   else if (in_dtype == LLM_F32 && dtype == LLM_BF16) HN_PLACE(float, __nv_bfloat16);
   else if (in_dtype == LLM_BF16 && dtype == LLM_BF16) HN_PLACE(__nv_bfloat16, __nv_bfloat16);
   else LLM_FAIL("rope_headnorm_place: unsupported dtypes in %d out %d", in_dtype, dtype);
+#undef HN_GO
 #undef HN_PLACE
   LLM_CHECK_LAUNCH("rope_headnorm_place");
   return LLM_OK;

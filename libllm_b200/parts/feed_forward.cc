@@ -232,10 +232,9 @@ class RoutedFeedForward : public FeedForward {
     if (s_own) {
       if (s.dtype != DType::F32 || s.rows != T || s.cols != hidden_ || s.ld != hidden_)
         LLM_THROW(Unsupported, "moe: the shared feed-forward must hand over dense 32-bit rows");
-      for (int p = 0; p < s.parts && !shared_gate_.empty(); ++p)
-        kernels::row_gate((const float *)s.data + (size_t)p * (size_t)s.part_stride,
-                          (float *)out.data + (size_t)(top_ + p) * (size_t)out.part_stride, (const float *)z.data + experts_, z.ld, (int)T,
-                          (int)hidden_, ctx.stream);
+      if (!shared_gate_.empty())
+        kernels::row_gate((const float *)s.data, s.part_stride, (float *)out.data + (size_t)top_ * (size_t)out.part_stride,
+                          out.part_stride, s.parts, (const float *)z.data + experts_, z.ld, (int)T, (int)hidden_, ctx.stream);
       for (int p = 0; p < s.parts && shared_gate_.empty(); ++p)
         LLM_CUDA(cudaMemcpyAsync((float *)out.data + (size_t)(top_ + p) * (size_t)out.part_stride,
                                  (const float *)s.data + (size_t)p * (size_t)s.part_stride, sizeof(float) * (size_t)(T * hidden_),

@@ -182,7 +182,7 @@ class LatentAttention : public Mixer {
       const int max_len = window_ > 0 ? std::min(std::max(ctx.max_kv_len, 1), window_ + 63) : std::max(ctx.max_kv_len, 1);
       const int ctas = std::max(1, T * ((n_heads_ + 31) / 32));
       const int want = std::max(1, (ctx.sm_count + ctas - 1) / ctas);
-      const int most = std::max(1, max_len / 256);
+      const int most = std::max(1, max_len / (window_ > 0 ? 128 : 256));      // under a window a token has few keys: shorter runs, more CTAs
       const int n_splits = std::max(1, std::min(std::min(want, most), 64));
       float *ws = nullptr;
       if (n_splits > 1) ws = ctx.arena->alloc_n<float>(kernels::latent_decode_floats(T, n_heads_, kv_rank_, n_splits));
