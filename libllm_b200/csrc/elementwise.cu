@@ -1068,8 +1068,8 @@ LLM_EXPORT int llm_head_gate(void *x, int dtype, long long ld, const float *gate
 // in_stride 0: the S streams are all equal to the one at x_in (a model's first layer).  With `rows`, output
 // row i is source row rows[i] and x_out holds the n_rows chosen rows only (out_stride apart per stream).
 // A row's result depends on that row alone; every sum has a fixed order.
-constexpr int HYPER_MAX_STREAMS = 8;
-template <typename TO, int THREADS, int VEC>
+constexpr int HYPER_MAX_STREAMS = 16;
+template <typename TO, int THREADS, int VEC, int MAXS>       // MAXS >= S: how many copies the unrolled loops provide for
 __global__ void __launch_bounds__(THREADS)
 hyper_mix_norm_kernel(const float *__restrict__ x_in, long long in_stride, float *__restrict__ x_out, long long out_stride, int S,
                       const float *__restrict__ delta, int n_parts, size_t part_stride, const float *__restrict__ col_scale,
@@ -1078,7 +1078,7 @@ hyper_mix_norm_kernel(const float *__restrict__ x_in, long long in_stride, float
                       const int *__restrict__ rows, int hidden) {
   extern __shared__ float row_buf[];   // hidden floats
   __shared__ float scratch[THREADS / 32 + 1];
-  __shared__ float s_mix[HYPER_MAX_STREAMS * HYPER_MAX_STREAMS], s_out[HYPER_MAX_STREAMS], s_in[HYPER_MAX_STREAMS];
+  __shared__ float s_mix[MAXS * MAXS], s_out[MAXS], s_in[MAXS];
   grid_dependents_launch();
   if (threadIdx.x < S * S) s_mix[threadIdx.x] = delta ? mix[threadIdx.x] : 0.f;       // weights: written when the model was loaded
   if (threadIdx.x < S) {
@@ -1092,9 +1092,9 @@ hyper_mix_norm_kernel(const float *__restrict__ x_in, long long in_stride, float
   const bool store = x_out != nullptr && (delta != nullptr || x_out != x_in || rows != nullptr || in_stride == 0);
   float ss = 0.f;
   for (int c = threadIdx.x * VEC; c < hidden; c += THREADS * VEC) {
-    float xs[HYPER_MAX_STREAMS][VEC];
+    float xs[MAXS][VEC];
 #pragma unroll
-    for (int s = 0; s < HYPER_MAX_STREAMS; ++s)
+    for (int s = 0; s < MAXS; ++s)
       if (s < S) {
         const float *p = x_in + (size_t)s * in_stride + (size_t)r * hidden + c;
         if (VEC == 4) {
@@ -1127,7 +1127,7 @@ hyper_mix_norm_kernel(const float *__restrict__ x_in, long long in_stride, float
 #pragma unroll
     for (int k = 0; k < VEC; ++k) u[k] = 0.f;
 #pragma unroll
-    for (int t = 0; t < HYPER_MAX_STREAMS; ++t)
+    for (int t = 0; t < MAXS; ++t)
       if (t < S) {
         float nv[VEC];
 #pragma unroll
@@ -1135,7 +1135,7 @@ hyper_mix_norm_kernel(const float *__restrict__ x_in, long long in_stride, float
           if (delta) {
             float a = 0.f;
 #pragma unroll
-            for (int s = 0; s < HYPER_MAX_STREAMS; ++s)
+            for (int s = 0; s < MAXS; ++s)
               if (s < S) a = fmaf(s_mix[s * S + t], xs[s][k], a);
             nv[k] = fmaf(s_out[t], y[k], a);
           } else {
@@ -1176,23 +1176,27 @@ static int launch_hyper(const float *x_in, long long in_stride, float *x_out, lo
   LLM_REQUIRE(smem <= 200 * 1024, "hyper_mix_norm: a row of %d values does not fit shared memory", hidden);
   const bool vec = hidden % 4 == 0 && in_stride % 4 == 0 && out_stride % 4 == 0 && part_stride % 4 == 0 && (uintptr_t)x_in % 16 == 0 &&
                    (uintptr_t)x_out % 16 == 0 && (uintptr_t)delta % 16 == 0;
-  if (vec && hidden >= 2048) {
-    // wide rows: 512 threads, so that a row of 2,048 values is one round of loads per thread
-    auto kern = hyper_mix_norm_kernel<TO, 512, 4>;
-    LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "hyper_mix_norm attribute");
-    llm_launch(kern, dim3(n_rows), dim3(512), smem, stream, x_in, in_stride, x_out, out_stride, S, delta, n_parts, part_stride, col_scale,
-               col_bias, mix, outw, inw, norm_w, eps, out, rows, hidden);
-  } else if (vec) {
-    auto kern = hyper_mix_norm_kernel<TO, 256, 4>;
-    LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "hyper_mix_norm attribute");
-    llm_launch(kern, dim3(n_rows), dim3(256), smem, stream, x_in, in_stride, x_out, out_stride, S, delta, n_parts, part_stride, col_scale,
-               col_bias, mix, outw, inw, norm_w, eps, out, rows, hidden);
+#define HYPER_GO(THREADS, VEC, MAXS)                                                                                               \
+  do {                                                                                                                             \
+    auto kern = hyper_mix_norm_kernel<TO, THREADS, VEC, MAXS>;                                                                     \
+    LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "hyper_mix_norm attribute");                                                       \
+    llm_launch(kern, dim3(n_rows), dim3(THREADS), smem, stream, x_in, in_stride, x_out, out_stride, S, delta, n_parts, part_stride, \
+               col_scale, col_bias, mix, outw, inw, norm_w, eps, out, rows, hidden);                                               \
+  } while (0)
+  // wide rows: 512 threads, so that a row of 2,048 values is one round of loads per thread; up to four copies (the
+  // usual case) keep the unrolled loops short
+  if (S <= 4) {
+    if (vec && hidden >= 2048) HYPER_GO(512, 4, 4);
+    else if (vec) HYPER_GO(256, 4, 4);
+    else HYPER_GO(256, 1, 4);
+  } else if (S <= 8) {
+    if (vec) HYPER_GO(256, 4, 8);
+    else HYPER_GO(256, 1, 8);
   } else {
-    auto kern = hyper_mix_norm_kernel<TO, 256, 1>;
-    LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "hyper_mix_norm attribute");
-    llm_launch(kern, dim3(n_rows), dim3(256), smem, stream, x_in, in_stride, x_out, out_stride, S, delta, n_parts, part_stride, col_scale,
-               col_bias, mix, outw, inw, norm_w, eps, out, rows, hidden);
+    if (vec) HYPER_GO(256, 4, 16);
+    else HYPER_GO(256, 1, 16);
   }
+#undef HYPER_GO
   LLM_CHECK_LAUNCH("hyper_mix_norm");
   return LLM_OK;
 }

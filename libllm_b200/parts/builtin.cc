@@ -812,7 +812,7 @@ class HyperBlock : public Block {
     ConfigReader r = reader_of(spec, "hyper block");
     streams_ = (int)r.integer("streams");
     hidden_ = r.integer("hidden");
-    if (streams_ > 8) LLM_THROW(Unsupported, "hyper block: %d residual streams are not supported (up to 8)", streams_);
+    if (streams_ > 16) LLM_THROW(Unsupported, "hyper block: %d residual streams are not supported (up to 16)", streams_);
     mixer_norm_ = build_as<Norm>("norm", r.object("mixer_norm"), env);
     mixer_ = build_as<Mixer>("mixer", r.object("mixer"), env);
     for (const char *k : {"mixer_in", "mixer_out", "mixer_mix"}) names_.push_back(r.string(k));

@@ -27,7 +27,7 @@ def ops():
 
 
 # ---------------------------------------------------------------- several copies of the residual stream
-@pytest.mark.parametrize("S_,T,H,parts", [(1, 5, 48, 1), (2, 9, 64, 3), (3, 4, 50, 1), (4, 33, 256, 2), (5, 7, 72, 4), (8, 3, 2048, 1)])
+@pytest.mark.parametrize("S_,T,H,parts", [(1, 5, 48, 1), (2, 9, 64, 3), (3, 4, 50, 1), (4, 33, 256, 2), (5, 7, 72, 4), (8, 3, 2048, 1), (13, 6, 40, 2), (16, 2, 128, 1)])
 @pytest.mark.parametrize("out_dtype", DTYPES)
 def test_pass_over_the_copies_of_the_stream(S_, T, H, parts, out_dtype):
     """The pending result of one sublayer moves all copies, the next sublayer's input is joined and normed: in place;
