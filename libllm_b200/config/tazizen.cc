@@ -75,7 +75,7 @@ Json parse_mixer(const Json &layer, const std::string &where) {
     if (heads % kv) r.fail("'heads' must be a multiple of 'kv_heads'");
     m.set("kv_heads", kv);
     m.set("vdim", r.integer_or("vdim", dim));
-    m.set("scale", r.number("scale", false));
+    m.set("scale", r.number_or("scale", 1.0 / std::sqrt((double)dim), false));
     m.set("rot", r.present("rot") ? parse_rot(r.object("rot"), where + ": mixer.rot", dim) : Json());
   } else if (type == "latent_attention") {
     const int64_t rot_dim = r.integer("rot_dim", 0);
@@ -83,7 +83,7 @@ Json parse_mixer(const Json &layer, const std::string &where) {
     m.set("vdim", r.integer_or("vdim", dim));
     m.set("kv_rank", r.integer("kv_rank"));
     m.set("q_rank", r.integer("q_rank"));
-    m.set("scale", r.number("scale", false));
+    m.set("scale", r.number_or("scale", 1.0 / std::sqrt((double)(dim + rot_dim)), false));
     if (rot_dim > 0) {
       Json rot = parse_rot(r.object("rot"), where + ": mixer.rot", rot_dim);
       if (rot.get("dims").as_int() != rot_dim) r.fail("'rot.dims' must equal 'rot_dim'");

@@ -105,7 +105,14 @@ def test_faults_are_named():
     broken(lambda c: c["loop"].update(stop=4), "'start' <= 'stop'")
     broken(lambda c: c.pop("norm"), "norm")
     broken(lambda c: c.update(streams=0), "streams")
-    broken(lambda c: c["layers"][0]["mixer"].pop("scale"), "scale")
+    broken(lambda c: c["layers"][0]["mixer"].pop("dim"), "dim")
+
+
+def test_a_mixer_without_a_scale_takes_the_usual_one():
+    c = copy.deepcopy(S.CONFIGS["T1"])
+    del c["layers"][0]["mixer"]["scale"], c["layers"][1]["mixer"]["scale"]
+    L = describe(c)["spec"]["layers"]
+    assert L[0]["mixer"]["scale"] == 16 ** -0.5 and abs(L[1]["mixer"]["scale"] - 24 ** -0.5) < 1e-15
 
 
 def test_the_caches_books_for_windows_of_looped_runs():
