@@ -75,6 +75,8 @@ Y3 = (2.5, 48, 4.0, 2.0)
 #     every expert chosen, one group.
 # T5: five copies, heads of 80 (a prompt kernel but no single-token kernel), three query heads to one key head, windows of
 #     exactly a page, a latent whose rows take the tensor-core kernels, two groups of which one is kept.
+# T7: wider: four copies, a loop of three layers at the start run twice, every tiled kernel at once (heads of 64 and 128, latent
+#     rows of 128 + 32 and 96 + 16), one of four groups kept.
 # T6: a loop at the end run once, four query heads to a key head with heads of 32 (the single-token kernel), a rotation of
 #     one pair, a scaled rotation in the latent layer, values wider than keys.
 CONFIGS: Dict[str, dict] = {
@@ -104,6 +106,12 @@ CONFIGS: Dict[str, dict] = {
                   layer(attn(8, 2, 32, 2, window=40, scale=0.9), None),
                   layer(attn(4, 1, 32, 16, window=150, vdim=48), moe(9, 2, 28, groups=(3, 1), shared=56))],
                  streams=2, loop=(1, 3, 1)),
+    "T7": config(500, 256, 1e-5,
+                 [layer(latent(8, 64, 32, 64, 128, 96, window=48, base=1e6), moe(16, 2, 64, groups=(4, 1), scale=1.0, shared=128)),
+                  layer(attn(8, 4, 128, 64, window=80, scaling=Y2), moe(16, 3, 64, groups=(2, 1), scale=2.0, shared=64)),
+                  layer(latent(4, 32, 16, 32, 96, 64, window=200, base=1e4, scaling=Y1), None),
+                  layer(attn(4, 4, 64, 64, window=31, vdim=64), moe(8, 2, 96))],
+                 streams=4, loop=(0, 3, 2)),
 }
 
 
